@@ -1,0 +1,59 @@
+// Host-side launchers of the sm_100a kernels.  Internal to the library: the public surfaces
+// are include/bitsqz_llm.hpp (C++ interface of the reference) and include/bitsqz_llm_c.h
+// (C ABI).  Every launcher enqueues work on `stream` and returns without synchronising.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace bsq {
+
+// ---- NF4 / NF4_DQ over a flat array (bsq_quant.cu) ----------------------------------------
+// d_deq_out (nullable): also write the dequantised values, which is what the reference's
+// compress path feeds into its error-correction stage (src/bitsqz_llm.cu:506-511).
+cudaError_t nf4_quantize(const float *d_x, uint64_t n, float *d_scales, uint8_t *d_data, float *d_deq_out, int sm_count,
+                         cudaStream_t stream);
+size_t nf4dq_scratch_bytes(uint64_t n);
+cudaError_t nf4dq_quantize(const float *d_x, uint64_t n, float *d_dq, uint8_t *d_scale_codes, uint8_t *d_data,
+                           float *d_deq_out, void *d_scratch, int sm_count, cudaStream_t stream);
+cudaError_t nf4_dequantize(const float *d_scales, const uint8_t *d_data, uint64_t n, float *d_out, int sm_count,
+                           cudaStream_t stream);
+cudaError_t nf4dq_dequantize(const float *d_dq, const uint8_t *d_scale_codes, const uint8_t *d_data, uint64_t n,
+                             float *d_out, int sm_count, cudaStream_t stream);
+
+// ---- per-row top-k (bsq_topk.cu) ------------------------------------------------------------
+// k = (uint16)roundf(cols * ratio) clamped to cols, at least 1 for ratio > 0; -1 for a ratio
+// outside [0, 1] (reference topk_cuda.cu:53-69).
+int topk_num_columns(uint16_t cols, float ratio);
+
+// Per row: the k entries of largest |x| ordered by (|x| descending, column ascending), NaN
+// ranking below every number.  d_idx / d_val are [rows][k].  d_residual (nullable): receives
+// the row with the selected entries set to +0.0f; may alias d_in (in-place separation).
+// d_status: device word that receives kStatus* bits.
+cudaError_t topk_rows(const float *d_in, float *d_residual, uint32_t rows, uint32_t cols, uint32_t k, uint16_t *d_idx,
+                      float *d_val, unsigned *d_status, int sm_count, cudaStream_t stream);
+
+// dense[row, idx] += val for every entry; indices >= cols are skipped and reported in d_status.
+cudaError_t topk_apply(const uint16_t *d_idx, const float *d_val, uint32_t rows, uint32_t cols, uint32_t k,
+                       float *d_dense, unsigned *d_status, cudaStream_t stream);
+
+// ---- fused front end of the no-SVD path (bsq_frontend.cu) -----------------------------------
+// outlier separation + NF4 or NF4_DQ of the remainder, reading the input once from HBM (the
+// NF4_DQ second pass re-reads it through L2).  Needs cols % 64 == 0, k <= 256 and a row that
+// fits shared memory; frontend_supported() says whether a shape qualifies.
+bool frontend_supported(uint32_t rows, uint32_t cols, uint32_t k);
+size_t frontend_scratch_bytes(uint32_t rows, uint32_t cols);
+// method: 11 = NF4 (d_scales_f32 used), 10 = NF4_DQ (d_dq, d_scale_codes used).
+cudaError_t frontend_quantize(int method, const float *d_in, uint32_t rows, uint32_t cols, uint32_t k, uint16_t *d_idx,
+                              float *d_val, float *d_scales_f32, float *d_dq, uint8_t *d_scale_codes, uint8_t *d_data,
+                              void *d_scratch, unsigned *d_status, int sm_count, cudaStream_t stream);
+
+// ---- residual / error helpers ---------------------------------------------------------------
+// e = a - b and *d_flag |= 1 when some |e| > FLT_EPSILON (reference src/bitsqz_llm.cu:164-184).
+cudaError_t residual_error(const float *d_a, const float *d_b, uint64_t n, float *d_e, unsigned *d_flag, int sm_count,
+                           cudaStream_t stream);
+
+int device_sm_count();
+
+}  // namespace bsq

@@ -1,0 +1,74 @@
+/*
+ * TEST INFRASTRUCTURE / one-off check.  The CUDA encoder does not run the reference's
+ * 16-way scan per element.  It maps v to one of 32 buckets with two fused multiply-adds
+ *     u = saturate(fma(v, 0.5, 0.5));  b = low 5 bits of bits(fma(u, 31, 1.5*2^23))
+ * and looks up (threshold T_b, base code B_b); code = B_b + (v >= T_b).  Because b is a
+ * monotone function of v and no bucket holds two thresholds, that equals "number of
+ * thresholds <= v", i.e. the reference scan wherever the scan is the 15-step function
+ * (all v < 2^23+1; see gen_nf4_thresholds.c).  This program builds the bucket table from
+ * the 15 thresholds with the same arithmetic, prints it, and compares the result with the
+ * literal scan (nf4_impl.cpp:73-86) for EVERY finite FP32 value below 2^23.
+ *
+ *   gcc -O2 -fopenmp -ffp-contract=off check_nf4_fast_encoder.c -o _ref/check_nf4_fast_encoder -lm
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+static const float L[16] = {
+    -1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+    -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+    0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
+    0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
+static const uint32_t TB[15] = {
+    0xbf591cd8u, 0xbf1c5270u, 0xbeeb847fu, 0xbeadea76u, 0xbe703cecu, 0xbe0d38bbu, 0xbd3a7870u, 0x3d22fb00u,
+    0x3df64863u, 0x3e5067e1u, 0x3e9582d5u, 0x3ec753fau, 0x3f006d04u, 0x3f248db0u, 0x3f5c89dau};
+
+static inline int scan(float v) {
+    int best = 0;
+    float be = fabsf(v - L[0]);
+    for (int i = 1; i < 16; ++i) {
+        float e = fabsf(v - L[i]);
+        if (e < be) { be = e; best = i; }
+    }
+    return best;
+}
+static inline float bits2f(uint32_t b) { float f; memcpy(&f, &b, 4); return f; }
+static inline uint32_t f2bits(float f) { uint32_t b; memcpy(&b, &f, 4); return b; }
+static inline int bucket(float v) {
+    float u = fmaf(v, 0.5f, 0.5f);
+    u = u < 0.0f ? 0.0f : (u > 1.0f ? 1.0f : u);
+    return (int)(f2bits(fmaf(u, 31.0f, 12582912.0f)) & 31u);
+}
+
+int main(void) {
+    float thr[32];
+    int base[32];
+    for (int b = 0; b < 32; ++b) { thr[b] = INFINITY; base[b] = -1; }
+    int owner[32] = {0};
+    for (int i = 0; i < 15; ++i) {
+        const int b = bucket(bits2f(TB[i]));
+        if (owner[b]) { printf("two thresholds in bucket %d\n", b); return 2; }
+        owner[b] = 1;
+        thr[b] = bits2f(TB[i]);
+    }
+    int running = 0;
+    for (int b = 0; b < 32; ++b) { base[b] = running; if (owner[b]) running++; }
+    printf("thr bits :");
+    for (int b = 0; b < 32; ++b) printf(" 0x%08x,", f2bits(thr[b]));
+    printf("\nbase     :");
+    for (int b = 0; b < 32; ++b) printf(" %d,", base[b]);
+    printf("\n");
+    unsigned long long bad = 0;
+#pragma omp parallel for schedule(static) reduction(+ : bad)
+    for (long long k = 0; k < (1ll << 32); ++k) {
+        const float v = bits2f((uint32_t)k);
+        if (!(fabsf(v) < 8388608.0f)) continue;          /* NaN, Inf and |v| >= 2^23: slow path */
+        const int b = bucket(v);
+        const int fast = base[b] + (v >= thr[b] ? 1 : 0);
+        if (fast != scan(v)) bad++;
+    }
+    printf("mismatches over all |v| < 2^23: %llu\n", bad);
+    return bad ? 1 : 0;
+}
