@@ -1,0 +1,337 @@
+"""Benchmark of the bitsqz_llm compress/decompress hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE.json configs[1]): one 4096 x 4096 FP32 activation matrix per step -- N(0,1) with
+0.1 % of the columns scaled by U[20,100] -- outlier top-k ratio 0.01, NF4_DQ, no SVD.  Data is
+seeded synthetic.  A step is one pass of the hot path (per-row outlier separation fused with the
+NF4_DQ quantiser) over one matrix.
+
+  value  FP32-input GB/s of the device stages with the input resident in HBM (CUDA events on the
+         launching stream, barrier + synchronize on both sides, max over ranks).  Successive steps
+         rotate over 4 different input matrices (256 MiB > the 126 MB L2), so no step finds its
+         input in L2 from the step before.
+  e2e    the same metric through the public bitsqz_llm_compress call with a pinned HOST matrix:
+         host->device copy of the input and device->host copy of the packed object inside the
+         timed region.
+  roofline      dominant kernel (pass 1: bulk row load, top-k selection, block maxima) from per-pass
+                CUDA events; algorithmic bytes per launch / duration against the measured HBM peak.
+  cpu_baseline  rank 0, N=1: the same workload on the host cores -- reference CPU NF4_DQ quantiser
+                (oracle/_ref, built from the reference's own sources) behind the oracle's top-k port
+                (the reference has no CPU top-k).
+
+With --impl reference the CPU pipeline above is what gets timed (the reference's GPU build is a parity
+oracle in tests, not a bench arm).  Multi-GPU: one process per GPU under torchrun, independent matrices
+per rank, no collective on the data path (weak scaling).
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+ROWS, COLS, OUTLIER_RATIO, METHOD = 4096, 4096, 0.01, 10
+NBUF = 4
+METRIC = "FP32-input GB/s, compress (outlier top-k 0.01 + NF4_DQ) of a 4096x4096 FP32 matrix"
+
+
+def make_matrix(seed):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((ROWS, COLS), dtype=np.float32)
+    ncol = max(1, int(round(0.001 * COLS)))
+    for c in rng.choice(COLS, size=ncol, replace=False):
+        x[:, c] *= np.float32(rng.uniform(20.0, 100.0))
+    return x
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, smax, reasons = [], [], set()
+        for line in out.splitlines():
+            f = [t.strip() for t in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [v for v in sm if v >= 0.5 * max(sm)] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_pipeline(orc_mod):
+    """(callable, kind, cores, description): outlier separation + NF4_DQ of one matrix on the host cores."""
+    oracle = orc_mod.Oracle()
+    try:
+        ref = orc_mod.RefCpu()
+    except (FileNotFoundError, OSError):
+        ref = None
+    k = oracle.topk_num_columns(COLS, OUTLIER_RATIO)
+
+    def step(x):
+        _, _, z = oracle.topk_rows(x, k, zero_selected=True)
+        if ref is not None:
+            ref.nf4dq_quantize(z)
+        else:
+            oracle.nf4dq_quantize(z)
+
+    cores = ref.max_threads() if ref is not None else oracle.max_threads()
+    kind = "reference" if ref is not None else "port"
+    desc = ("NF4_DQ: reference legacy CPU quantiser (OpenMP); top-k: oracle port, the reference has none on CPU"
+            if ref is not None else "oracle port (OpenMP) of top-k separation + NF4_DQ")
+    return step, kind, cores, desc
+
+
+def run_reference(args, rank):
+    """--impl reference: the CPU implementation of the path on this box's host cores."""
+    if rank != 0:
+        return
+    orc = entry.load_oracle()
+    step, kind, cores, desc = cpu_pipeline(orc)
+    xs = [make_matrix(100 + i) for i in range(2)]
+    for i in range(max(1, min(args.warmup, 2))):
+        step(xs[i % 2])
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        step(xs[i % 2])
+    dt = time.perf_counter() - t0
+    gbs = ROWS * COLS * 4 * args.steps / dt / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "configs[1]: 4096x4096 FP32, outlier_topk=0.01, NF4_DQ, no SVD", "rows": ROWS, "cols": COLS},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind,
+                         "sample": f"{args.steps} full matrices per run; {desc}"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+
+    pkg = entry.load_package()
+    L = pkg.lib()
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    n = ROWS * COLS
+    k = L.bsq_topk_num_columns(COLS, OUTLIER_RATIO)
+    nb = n // 64
+    host = [make_matrix(1000 * rank + i) for i in range(NBUF)]
+    d_in = [torch.from_numpy(h).cuda() for h in host]
+    d_idx = torch.zeros((ROWS, k), dtype=torch.int16, device="cuda")
+    d_val = torch.zeros((ROWS, k), dtype=torch.float32, device="cuda")
+    d_dq = torch.zeros(4, dtype=torch.float32, device="cuda")
+    d_codes = torch.zeros(nb, dtype=torch.uint8, device="cuda")
+    d_data = torch.zeros(n // 2, dtype=torch.uint8, device="cuda")
+    d_scr = torch.zeros(L.bsq_frontend_scratch_bytes(ROWS, COLS), dtype=torch.uint8, device="cuda")
+    d_st = torch.zeros(4, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def stage(i):
+        rc = L.bsq_frontend_quantize(METHOD, d_in[i % NBUF].data_ptr(), ROWS, COLS, k, d_idx.data_ptr(), d_val.data_ptr(),
+                                     None, d_dq.data_ptr(), d_codes.data_ptr(), d_data.data_ptr(), d_scr.data_ptr(),
+                                     d_st.data_ptr(), stream)
+        if rc != 0:
+            raise RuntimeError("bsq_frontend_quantize failed")
+
+    # ---- device-stage throughput ----
+    for i in range(args.warmup):
+        stage(i)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        stage(i)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    if int(d_st[0]) != 0:
+        raise RuntimeError("kernel status word set: %d" % int(d_st[0]))
+
+    # ---- per-pass durations for the roofline (events between the two kernels) ----
+    ms_pass = (C.c_float * 2)()
+    p1, p2 = [], []
+    for i in range(max(8, min(args.steps, 24))):
+        rc = L.bsq_frontend_quantize_timed(METHOD, d_in[i % NBUF].data_ptr(), ROWS, COLS, k, d_idx.data_ptr(), d_val.data_ptr(),
+                                           None, d_dq.data_ptr(), d_codes.data_ptr(), d_data.data_ptr(), d_scr.data_ptr(),
+                                           d_st.data_ptr(), stream, ms_pass)
+        if rc != 0:
+            raise RuntimeError("bsq_frontend_quantize_timed failed")
+        p1.append(ms_pass[0])
+        p2.append(ms_pass[1])
+    ms_p1, ms_p2 = statistics.mean(p1), statistics.mean(p2)
+
+    # ---- end to end through the public call: pinned host input, packed object back on the host ----
+    pinned = [torch.from_numpy(h).pin_memory() for h in host]
+    assert L.bsq_compress_initialize(ROWS, COLS, OUTLIER_RATIO, 0.0, -1, 1, pkg.NONE, pkg.NONE, METHOD, pkg.INPUT_HOST) == 0
+
+    def e2e_step(i):
+        out = C.c_void_p(None)
+        if L.bsq_compress(pinned[i % NBUF].data_ptr(), C.byref(out), None) != 0:
+            raise RuntimeError("bitsqz_llm_compress failed")
+        size = int(L.bsq_get_packed_size(out))
+        L.bsq_free(out)
+        return size
+    for i in range(args.warmup):
+        packed_size = e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    L.bsq_compress_release()
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- decompress (device stages: NF4_DQ dequantise + outlier scatter-add), reported beside ----
+    d_out = torch.zeros((ROWS, COLS), dtype=torch.float32, device="cuda")
+    outs = [torch.zeros((ROWS, COLS), dtype=torch.float32, device="cuda") for _ in range(NBUF)]
+
+    def dstage(i):
+        o = outs[i % NBUF]
+        L.bsq_nf4dq_dequantize(d_dq.data_ptr(), d_codes.data_ptr(), d_data.data_ptr(), n, o.data_ptr(), stream)
+        L.bsq_topk_apply(d_idx.data_ptr(), d_val.data_ptr(), ROWS, COLS, k, o.data_ptr(), d_st.data_ptr(), stream)
+    for i in range(args.warmup):
+        dstage(i)
+    barrier()
+    d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    d0.record()
+    for i in range(args.steps):
+        dstage(i)
+    d1.record()
+    barrier()
+    ms_dec = d0.elapsed_time(d1)
+    del d_out
+
+    # ---- max over ranks ----
+    times = torch.tensor([ms_total, e2e_s * 1e3, ms_dec, ms_p1, ms_p2], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms, ms_dec, ms_p1, ms_p2 = [float(v) for v in times.cpu()]
+
+    if rank == 0:
+        in_bytes = n * 4
+        value = world * in_bytes * args.steps / (ms_total * 1e-3) / 1e9
+        e2e_value = world * in_bytes * args.steps / (e2e_ms * 1e-3) / 1e9
+        dec_value = world * in_bytes * args.steps / (ms_dec * 1e-3) / 1e9
+        peak, peak_kind = measured_peaks()
+        # algorithmic bytes: pass 1 reads the matrix once and writes k (u16, f32) pairs per row and one
+        # float per 64-element block; the whole stage adds the nibbles and one scale byte per block
+        bytes_p1 = in_bytes + ROWS * k * 6 + nb * 4
+        bytes_stage = in_bytes + ROWS * k * 6 + n // 2 + nb + 4
+        ach_p1 = bytes_p1 / (ms_p1 * 1e-3) / 1e9
+        ach_stage = bytes_stage / ((ms_total / args.steps) * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "configs[1]: 4096x4096 FP32 device matrix, outlier_topk=0.01 (k=41/row), NF4_DQ, no SVD",
+                       "rows": ROWS, "cols": COLS, "k": int(k), "parallelism": f"independent matrices x{world}",
+                       "l2": f"inputs rotate over {NBUF} x 64 MiB matrices (256 MiB > 126 MB L2)"},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": int(packed_size),
+                    "api": "bitsqz_llm_compress, BITSQZ_LLM_INPUT_HOST, pinned input"},
+            "decompress": {"value": dec_value, "unit": "GB/s (FP32 output)", "ms_per_step": ms_dec / args.steps,
+                           "stages": "nf4dq dequantise + outlier scatter-add, device resident"},
+            "gpu_launches": 2 * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "frontend_pass1_kernel<256,true>", "achieved": ach_p1, "peak": peak,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": ach_p1 / peak, "traffic": None,
+                         "ms_per_launch": ms_p1, "pass2_ms_per_launch": ms_p2,
+                         "stage": {"achieved": ach_stage, "frac": ach_stage / peak, "bytes": bytes_stage}},
+            "clocks": clocks,
+        }
+        if world == 1:
+            orc = entry.load_oracle()
+            step, kind, cores, desc = cpu_pipeline(orc)
+            step(host[0])
+            reps, t0 = 0, time.perf_counter()
+            while reps < 3 or (time.perf_counter() - t0 < 10.0 and reps < 200):
+                step(host[reps % NBUF])
+                reps += 1
+            dt = time.perf_counter() - t0
+            line["cpu_baseline"] = {"value": in_bytes * reps / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
+                                    "sample": f"{reps} full matrices in {dt:.1f} s; {desc}"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -47,7 +47,8 @@ size_t frontend_scratch_bytes(uint32_t rows, uint32_t cols);
 // method: 11 = NF4 (d_scales_f32 used), 10 = NF4_DQ (d_dq, d_scale_codes used).
 cudaError_t frontend_quantize(int method, const float *d_in, uint32_t rows, uint32_t cols, uint32_t k, uint16_t *d_idx,
                               float *d_val, float *d_scales_f32, float *d_dq, uint8_t *d_scale_codes, uint8_t *d_data,
-                              void *d_scratch, unsigned *d_status, int sm_count, cudaStream_t stream);
+                              void *d_scratch, unsigned *d_status, int sm_count, cudaStream_t stream,
+                              cudaEvent_t *events = nullptr);   // events[3]: before pass 1, between, after pass 2
 
 // ---- residual / error helpers ---------------------------------------------------------------
 // e = a - b and *d_flag |= 1 when some |e| > FLT_EPSILON (reference src/bitsqz_llm.cu:164-184).
@@ -55,5 +56,22 @@ cudaError_t residual_error(const float *d_a, const float *d_b, uint64_t n, float
                            cudaStream_t stream);
 
 int device_sm_count();
+bool topk_rows_fit_smem(const void *d_in, const void *d_residual, uint32_t cols, uint32_t k);
+
+// ---- randomized low-rank SVD and reconstruction (bsq_svd.cu, bsq_gemm.cu) -------------------
+// Replaces svd_lowrank_cuda_initialize / svd_lowrank_cuda / svd_lowrank_cuda_release
+// (modules/svd_lowrank_cuda/src/svd_lowrank_cuda.cu:541-581) and reconstruct_lowrank_cuda
+// (modules/reconstruct_lowrank_cuda/src/reconstruct_lowrank_cuda.cu:153-171).
+struct SvdWorkspace;
+SvdWorkspace *svd_workspace_create(int m, int n, int k, int niter, int sm_count);
+void svd_workspace_destroy(SvdWorkspace *ws);
+// A row-major m x n -> U (m x k row-major), S (k, descending), V (n x k row-major).
+cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d_S, float *d_V,
+                        unsigned long long seed, unsigned *d_status, cudaStream_t stream);
+// out = (U diag(S)) V^T, row-major m x n.  d_minuend (nullable): write minuend - out instead and
+// OR 1 into *d_flag when some |difference| > FLT_EPSILON.
+cudaError_t reconstruct_lowrank(const float *d_U, const float *d_S, const float *d_V, int m, int n, int k,
+                                const float *d_minuend, float *d_out, unsigned *d_flag, int sm_count,
+                                cudaStream_t stream);
 
 }  // namespace bsq

@@ -95,10 +95,10 @@ __global__ void __launch_bounds__(kThreads) absmax_flat_kernel(const float *__re
 // ---- encode: NF4 (DQ == false: computes its own absmax) or NF4_DQ pass 2 -----------------
 template <bool DQ, bool WRITE_DEQ>
 __global__ void __launch_bounds__(kThreads)
-    encode_flat_kernel(const float *__restrict__ x, uint64_t n, bool vec, const float *__restrict__ absmax_in,
+    encode_flat_kernel(const float *x, uint64_t n, bool vec, const float *__restrict__ absmax_in,
                        const unsigned *__restrict__ gmax_bits, float *__restrict__ scales_f32,
                        uint8_t *__restrict__ scale_codes, float *__restrict__ dq_out, uint8_t *__restrict__ data,
-                       float *__restrict__ deq_out) {
+                       float *deq_out) {   // deq_out may alias x (in-place write-back)
     const int lane = threadIdx.x & 31;
     const uint64_t warp = (uint64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
     const uint64_t nwarps = (uint64_t)gridDim.x * (kThreads / 32);

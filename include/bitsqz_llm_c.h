@@ -1,0 +1,118 @@
+/*
+ * bitsqz_llm -- C ABI of the compress/decompress hot path (plain pointers and sizes only).
+ *
+ * The reference library has C++ linkage (include/bitsqz_llm.hpp has no extern "C" and
+ * overloads bitsqz_llm_compress), so a foreign-function binding cannot name its symbols
+ * portably.  This header gives every entry point of that interface, and every stage function
+ * of the reference's four CUDA modules that the path is built from, a C name.  The library
+ * exports both sets: the C++ symbols for callers that relink, these for cgo / ctypes / JNI.
+ *
+ * Conventions: int results are 0 on success and 1 on failure (the reference's convention);
+ * nothing throws; `d_` pointers are device memory of the calling thread's current CUDA device;
+ * `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream); stage functions
+ * only enqueue work on `stream` and do not synchronise.  Enum arguments are passed as int with
+ * the values of bitsqz_llm.hpp: method -1 none, 10 NF4_DQ, 11 NF4; location 0 host, 1 device.
+ */
+#ifndef BITSQZ_LLM_C_H
+#define BITSQZ_LLM_C_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+struct bitsqz_llm_array;                /* 200-byte header + payload, see bitsqz_llm.hpp */
+struct bitsqz_llm_compress_profile;     /* seven doubles, see bitsqz_llm.hpp */
+
+/* ---- the public interface (include/bitsqz_llm.hpp:95-141 of the reference) ---------------- */
+
+/* bitsqz_llm_compress_initialize, include/bitsqz_llm.hpp:95-105 */
+int bsq_compress_initialize(uint16_t num_rows, uint16_t num_columns, float outlier_topk_ratio,
+                            float error_correction_topk_ratio, int svd_ranks, int svd_niters, int svd_uv_format,
+                            int svd_s_format, int quantization_only_format, int input_location);
+/* bitsqz_llm_compress_release, :107 */
+void bsq_compress_release(void);
+/* bitsqz_llm_decompress_initialize, :109-117 */
+int bsq_decompress_initialize(uint16_t num_rows, uint16_t num_columns, float outlier_topk_ratio,
+                              float error_correction_topk_ratio, int svd_ranks, int svd_uv_format, int svd_s_format,
+                              int quantization_only_format);
+/* bitsqz_llm_decompress_release, :119 */
+void bsq_decompress_release(void);
+/* bitsqz_llm_compress, :121-124.  *out must be NULL on entry; profile may be NULL. */
+int bsq_compress(const float *row_major_matrix, struct bitsqz_llm_array **out, void *profile);
+/* bitsqz_llm_decompress, :132-135 */
+int bsq_decompress(const struct bitsqz_llm_array *compressed, float *d_dst, uint32_t dst_num_elements);
+/* bitsqz_llm_get_packed_size, :137 */
+uint64_t bsq_get_packed_size(const struct bitsqz_llm_array *compressed);
+/* load_bitsqz_llm_from_buffer, :139 */
+struct bitsqz_llm_array *bsq_load_from_buffer(const void *buffer, uint64_t buffer_size);
+/* bitsqz_llm_free, :141 */
+void bsq_free(struct bitsqz_llm_array *compressed);
+
+/* ---- per-row top-k (modules/topk_cuda/include/topk_cuda.cuh:47-107) ----------------------- */
+
+/* topk_compute_num_topk_columns, topk_cuda.cuh:47; -1 for a ratio outside [0, 1] */
+int bsq_topk_num_columns(uint16_t num_columns, float topk_ratio);
+/* topk_extraction (d_residual NULL) / topk_separation (d_residual = zeroed copy, may equal d_in),
+ * topk_cuda.cuh:68-76.  d_idx, d_val: [rows][k], ordered by (|x| descending, column ascending).
+ * d_status: one device word that receives error bits (0 = fine); may be NULL. */
+int bsq_topk_rows(const float *d_in, float *d_residual, uint32_t rows, uint32_t cols, uint32_t k, uint16_t *d_idx,
+                  float *d_val, uint32_t *d_status, void *stream);
+/* topk_apply, topk_cuda.cuh:83-86: dense[row, idx] += val */
+int bsq_topk_apply(const uint16_t *d_idx, const float *d_val, uint32_t rows, uint32_t cols, uint32_t k, float *d_dense,
+                   uint32_t *d_status, void *stream);
+
+/* ---- NF4 / NF4_DQ (modules/quantization_cuda/include/quantization_cuda/quantization_cuda.cuh:58-112) */
+
+/* quantization_cuda_compress with an NF4 array, quantization_cuda.cuh:86-89.  d_scales: ceil(n/64)
+ * floats, d_data: ceil(n/2) bytes, d_deq_out: NULL or n floats (dequantised values, may equal d_x). */
+int bsq_nf4_quantize(const float *d_x, uint64_t n, float *d_scales, uint8_t *d_data, float *d_deq_out, void *stream);
+/* bytes of device scratch bsq_nf4dq_quantize needs for n elements */
+size_t bsq_nf4dq_scratch_bytes(uint64_t n);
+/* quantization_cuda_compress with an NF4_DQ array.  d_dq: 1 float, d_scale_codes: ceil(n/64) bytes. */
+int bsq_nf4dq_quantize(const float *d_x, uint64_t n, float *d_dq, uint8_t *d_scale_codes, uint8_t *d_data,
+                       float *d_deq_out, void *d_scratch, void *stream);
+/* quantization_cuda_decompress, quantization_cuda.cuh:91-94 */
+int bsq_nf4_dequantize(const float *d_scales, const uint8_t *d_data, uint64_t n, float *d_out, void *stream);
+int bsq_nf4dq_dequantize(const float *d_dq, const uint8_t *d_scale_codes, const uint8_t *d_data, uint64_t n,
+                         float *d_out, void *stream);
+
+/* ---- fused outlier separation + quantiser: the no-SVD branch of bitsqz_llm_compress
+ * (src/bitsqz_llm.cu:1045-1056,1183-1195) as one stage --------------------------------------- */
+int bsq_frontend_supported(uint32_t rows, uint32_t cols, uint32_t k);
+size_t bsq_frontend_scratch_bytes(uint32_t rows, uint32_t cols);
+int bsq_frontend_quantize(int method, const float *d_in, uint32_t rows, uint32_t cols, uint32_t k, uint16_t *d_idx,
+                          float *d_val, float *d_scales_f32, float *d_dq, uint8_t *d_scale_codes, uint8_t *d_data,
+                          void *d_scratch, uint32_t *d_status, void *stream);
+
+/* Same call, bracketed by CUDA events on `stream`: ms_pass[0] = pass 1 (selection + block maxima, or the
+ * whole NF4 kernel), ms_pass[1] = pass 2 (NF4_DQ encode; 0 for NF4).  Synchronises; for measurement. */
+int bsq_frontend_quantize_timed(int method, const float *d_in, uint32_t rows, uint32_t cols, uint32_t k,
+                                uint16_t *d_idx, float *d_val, float *d_scales_f32, float *d_dq,
+                                uint8_t *d_scale_codes, uint8_t *d_data, void *d_scratch, uint32_t *d_status,
+                                void *stream, float *ms_pass);
+
+/* ---- error stage (src/bitsqz_llm.cu:164-184,375-423): e = a - b, *d_flag |= any(|e| > FLT_EPSILON) */
+int bsq_residual_error(const float *d_a, const float *d_b, uint64_t n, float *d_e, uint32_t *d_flag, void *stream);
+
+/* ---- low-rank stages ------------------------------------------------------------------------- */
+
+/* svd_lowrank_cuda_initialize + svd_lowrank_cuda + svd_lowrank_cuda_release
+ * (modules/svd_lowrank_cuda/include/svd_lowrank_cuda/svd_lowrank_cuda.cuh:54-68) in one call:
+ * rank-k randomized SVD of the row-major m x n matrix d_A.  d_U: m x k, d_S: k, d_V: n x k. */
+int bsq_svd_lowrank(const float *d_A, int m, int n, int k, int niter, unsigned long long seed, float *d_U, float *d_S,
+                    float *d_V, void *stream);
+/* reconstruct_lowrank_cuda (reconstruct_lowrank_cuda.cuh:73-78): d_out = (U diag(S)) V^T.
+ * d_minuend non-NULL: d_out = d_minuend - (U diag(S)) V^T and *d_flag |= any(|d_out| > FLT_EPSILON). */
+int bsq_reconstruct(const float *d_U, const float *d_S, const float *d_V, int m, int n, int k, const float *d_minuend,
+                    float *d_out, uint32_t *d_flag, void *stream);
+
+/* library build tag: "sm_100a" plus the compile date */
+const char *bsq_build_info(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BITSQZ_LLM_C_H */
