@@ -163,6 +163,8 @@ def main():
     ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--stage-only", action="store_true",
+                    help="run only the device-stage loop (for profiler captures); prints no bench line")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -222,6 +224,11 @@ def main():
     e1.record()
     barrier()
     ms_total = e0.elapsed_time(e1)
+    if args.stage_only:
+        if rank == 0:
+            sampler.stop()
+            print(json.dumps({"stage_only": True, "ms_per_step": ms_total / args.steps}))
+        return
     if int(d_st[0]) != 0:
         raise RuntimeError("kernel status word set: %d" % int(d_st[0]))
 

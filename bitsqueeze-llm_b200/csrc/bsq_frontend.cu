@@ -94,7 +94,7 @@ __device__ __forceinline__ void row_encode(const float *row, unsigned cols, cons
             scale_codes_out[oi4 >> 4] = (uint8_t)code;
         }
         const float inv = __fdiv_rn(1.0f, scale);
-        const unsigned slow_blocks = DQ ? __ballot_sync(kFullMask, __fmul_rn(blk_absmax, inv) >= 8388608.0f) : 0u;
+        const unsigned slow_blocks = __ballot_sync(kFullMask, !(__fmul_rn(blk_absmax, inv) < 8388608.0f));
 #pragma unroll
         for (int fi = 0; fi < kChunkIters; ++fi) {
             const int j = fi * 2 + (lane >> 4);
@@ -103,7 +103,7 @@ __device__ __forceinline__ void row_encode(const float *row, unsigned cols, cons
             unsigned c[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) c[q] = lut.encode(__fmul_rn(v[q], invb));
-            if (DQ && ((slow_blocks >> j) & 1u)) {
+            if ((slow_blocks >> j) & 1u) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) c[q] = nf4_code_scan(__fmul_rn(v[q], invb));
             }

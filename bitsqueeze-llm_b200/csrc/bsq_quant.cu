@@ -134,9 +134,10 @@ __global__ void __launch_bounds__(kThreads)
             }
         }
         const float inv = __fdiv_rn(1.0f, scale);
-        // A scaled value can only leave the encoder's exact range when a DQ block fell back
-        // to scale 1.0 while holding a huge element; such blocks take the literal scan.
-        const unsigned slow_blocks = DQ ? __ballot_sync(kFullMask, __fmul_rn(blk_absmax, inv) >= 8388608.0f) : 0u;
+        // A scaled value leaves the encoder's exact range (|v| < 2^23) only in two corners: a DQ
+        // block that fell back to scale 1.0 while holding a huge element, and a block whose scale
+        // is so small (denormal) that 1/scale overflows; such blocks take the literal scan.
+        const unsigned slow_blocks = __ballot_sync(kFullMask, !(__fmul_rn(blk_absmax, inv) < 8388608.0f));
 
 #pragma unroll
         for (int it = 0; it < 4; ++it) {
@@ -146,7 +147,7 @@ __global__ void __launch_bounds__(kThreads)
             unsigned c[8];
 #pragma unroll
             for (int q = 0; q < 8; ++q) c[q] = lut.encode(__fmul_rn(sanitize(r[it].v[q]), invb));
-            if (DQ && ((slow_blocks >> j) & 1u)) {
+            if ((slow_blocks >> j) & 1u) {
 #pragma unroll
                 for (int q = 0; q < 8; ++q) c[q] = nf4_code_scan(__fmul_rn(sanitize(r[it].v[q]), invb));
             }
