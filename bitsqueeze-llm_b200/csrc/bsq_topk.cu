@@ -19,8 +19,8 @@ namespace bsq {
 namespace {
 
 // ---- rows that fit shared memory: cols % 4 == 0, k <= kCandCap, 16-byte aligned rows ----------
-template <int NT>
-__global__ void __launch_bounds__(NT)
+template <int NT, int IT>
+__global__ void __launch_bounds__(NT, 1536 / NT)
     topk_rows_smem_kernel(const float *__restrict__ in, float *residual, unsigned rows, unsigned cols, unsigned k,
                           uint16_t *__restrict__ out_idx, float *__restrict__ out_val, unsigned *status) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -35,6 +35,7 @@ __global__ void __launch_bounds__(NT)
     }
     __syncthreads();
     unsigned phase = 0;
+    float hint = 0.0f;
     for (unsigned r = blockIdx.x; r < rows; r += gridDim.x) {
         if (tid == 0) {
             mbar_expect_tx(&bar, bytes);
@@ -42,7 +43,11 @@ __global__ void __launch_bounds__(NT)
         }
         if (!mbar_wait_bounded(&bar, phase, status)) return;
         phase ^= 1u;
-        topk_row<NT>(row, cols, k, s, out_idx + (size_t)r * k, out_val + (size_t)r * k, residual != nullptr);
+        unsigned m4[IT];
+        const unsigned gb = row_thread_max<NT, IT>(row, cols, m4);
+        const bool special = __syncthreads_or(gb >= 0x7f800000u) != 0;
+        hint = topk_row<NT, IT>(row, cols, k, s, out_idx + (size_t)r * k, out_val + (size_t)r * k, residual != nullptr, gb, m4,
+                            special, hint);
         if (residual != nullptr) {
             fence_proxy_async_smem();
             __syncthreads();
@@ -221,29 +226,34 @@ int topk_num_columns(uint16_t cols, float ratio) {
 // Shared-memory bytes the row kernel needs, and the thread count that suits the row length.
 static size_t smem_row_bytes(uint32_t cols) { return (size_t)cols * 4 + sizeof(TopkScratch); }
 static int smem_row_threads(uint32_t cols) { return cols <= 4096 ? 256 : (cols <= 16384 ? 512 : 1024); }
+static cudaError_t prefer_max_smem(const void *kernel, size_t smem) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return err;
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
 
 bool topk_rows_fit_smem(const void *d_in, const void *d_residual, uint32_t cols, uint32_t k) {
     if (cols % 4 != 0 || k == 0 || k > (uint32_t)kCandCap) return false;
     if (k > (uint32_t)smem_row_threads(cols)) return false;
-    if (smem_row_bytes(cols) > 200 * 1024) return false;
+    if (smem_row_bytes(cols) > 200 * 1024 || cols > 4u * (uint32_t)smem_row_threads(cols) * kMaxRowIters) return false;
     if (reinterpret_cast<uintptr_t>(d_in) % 16 != 0) return false;
     if (d_residual && reinterpret_cast<uintptr_t>(d_residual) % 16 != 0) return false;
     return true;
 }
 
-template <int NT>
+template <int NT, int IT>
 static cudaError_t launch_smem(const float *d_in, float *d_residual, uint32_t rows, uint32_t cols, uint32_t k,
                                uint16_t *d_idx, float *d_val, unsigned *d_status, int sm_count, cudaStream_t stream) {
     const size_t smem = smem_row_bytes(cols);
-    cudaError_t err = cudaFuncSetAttribute(topk_rows_smem_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t err = prefer_max_smem(reinterpret_cast<const void *>(topk_rows_smem_kernel<NT, IT>), smem);
     if (err != cudaSuccess) return err;
     int per_sm = 0;
-    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, topk_rows_smem_kernel<NT>, NT, smem);
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, topk_rows_smem_kernel<NT, IT>, NT, smem);
     if (err != cudaSuccess) return err;
     if (per_sm < 1) per_sm = 1;
     unsigned grid = (unsigned)sm_count * (unsigned)per_sm;      // persistent: every CTA resident
     if (grid > rows) grid = rows;
-    topk_rows_smem_kernel<NT><<<grid, NT, smem, stream>>>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status);
+    topk_rows_smem_kernel<NT, IT><<<grid, NT, smem, stream>>>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status);
     return cudaGetLastError();
 }
 
@@ -257,11 +267,16 @@ cudaError_t topk_rows(const float *d_in, float *d_residual, uint32_t rows, uint3
     }
     if (!d_idx || !d_val) return cudaErrorInvalidValue;
     if (topk_rows_fit_smem(d_in, d_residual, cols, k)) {
-        switch (smem_row_threads(cols)) {
-            case 256: return launch_smem<256>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status, sm_count, stream);
-            case 512: return launch_smem<512>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status, sm_count, stream);
-            default: return launch_smem<1024>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status, sm_count, stream);
+        const int nt = smem_row_threads(cols);
+        const bool few = cols <= 16u * (uint32_t)nt;          // at most 4 float4 per thread
+#define BSQ_LAUNCH(NT_) (few ? launch_smem<NT_, 4>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status, sm_count, stream) \
+                             : launch_smem<NT_, 8>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status, sm_count, stream))
+        switch (nt) {
+            case 256: return BSQ_LAUNCH(256);
+            case 512: return BSQ_LAUNCH(512);
+            default: return BSQ_LAUNCH(1024);
         }
+#undef BSQ_LAUNCH
     }
     unsigned grid = (unsigned)sm_count * 8u;
     if (grid > rows) grid = rows;

@@ -23,6 +23,13 @@
 
 #include "bsq_device.cuh"
 
+#ifdef BSQ_TRACE
+static __device__ long long g_trace_topk[16];
+#define BSQ_TT(slot) do { if (blockIdx.x == 5 && threadIdx.x == 0) g_trace_topk[slot] = clock64(); } while (0)
+#else
+#define BSQ_TT(slot) do { } while (0)
+#endif
+
 namespace bsq {
 
 constexpr int kCandCap = 256;              // candidate slots; also the largest k these routines take
@@ -30,9 +37,9 @@ constexpr int kCandCap = 256;              // candidate slots; also the largest 
 struct TopkScratch {                       // per-CTA shared-memory scratch
     unsigned hist[256];
     unsigned long long cand[kCandCap];
-    unsigned short worklist[1024];
+    unsigned dirty[256];                   // one bit per float4 of the row: holds an entry that was zeroed
     unsigned count;                        // candidates appended
-    unsigned nwork;                        // worklist entries
+    unsigned kth_bits;                     // |x| bits of the k-th entry of the row just finished
     unsigned sel_bin;                      // histogram search result
     unsigned sel_need;
     unsigned sel_ok;
@@ -135,7 +142,10 @@ __device__ __forceinline__ void sort_emit_warp(TopkScratch &s, float *row, unsig
             const unsigned col = 0xFFFFu - (unsigned)(a[slot] & 0xFFFFull);
             out_idx[r] = (uint16_t)col;
             out_val[r] = row[col];
-            if (zero_selected) row[col] = 0.0f;
+            if (zero_selected) {
+                row[col] = 0.0f;
+                atomicOr(&s.dirty[col >> 7], 1u << ((col >> 2) & 31u));
+            }
         }
     }
 }
@@ -150,7 +160,7 @@ __device__ __forceinline__ void sort_emit_dispatch(TopkScratch &s, float *row, u
 // Exact path.  `row` may be any generic pointer (shared or global).  All threads of the CTA
 // call it; k <= kCandCap; cols <= 65535.  Ends with a __syncthreads().
 template <int NT>
-__device__ void topk_exact(float *row, unsigned cols, unsigned k, TopkScratch &s, uint16_t *out_idx, float *out_val,
+__device__ __noinline__ void topk_exact(float *row, unsigned cols, unsigned k, TopkScratch &s, uint16_t *out_idx, float *out_val,
                            bool zero_selected) {
     const int tid = threadIdx.x;
     unsigned long long prefix = 0;
@@ -184,51 +194,62 @@ __device__ void topk_exact(float *row, unsigned cols, unsigned k, TopkScratch &s
     __syncthreads();
 }
 
-// Fast path with fallback.  `row` is a shared-memory row of `cols` floats, cols % 4 == 0,
-// 16-byte aligned; k <= min(kCandCap, NT).  All threads call it; ends with __syncthreads().
-template <int NT>
-__device__ void topk_row(float *row, unsigned cols, unsigned k, TopkScratch &s, uint16_t *out_idx, float *out_val,
-                         bool zero_selected) {
-    const int tid = threadIdx.x;
+// Per-thread maximum of the |x| bit patterns of a shared-memory row, float4 i = f * NT + tid.
+// m4[f] keeps the maximum of each float4 (0 past the end of the row).  A result >= 0x7f800000
+// means the thread saw an Inf or NaN.
+constexpr int kMaxRowIters = 8;
+template <int NT, int IT>
+__device__ __forceinline__ unsigned row_thread_max(const float *row, unsigned cols, unsigned (&m4)[IT]) {
     const unsigned f4 = cols >> 2;
-    const float4 *row4 = reinterpret_cast<const float4 *>(row);
+    const uint4 *row4 = reinterpret_cast<const uint4 *>(row);
+    unsigned g = 0;
+#pragma unroll
+    for (int f = 0; f < IT; ++f) {
+        const unsigned i = f * NT + threadIdx.x;
+        unsigned m = 0;
+        if (i < f4) {
+            const uint4 a = row4[i];
+            m = max(max(a.x & 0x7fffffffu, a.y & 0x7fffffffu), max(a.z & 0x7fffffffu, a.w & 0x7fffffffu));
+        }
+        m4[f] = m;
+        g = max(g, m);
+    }
+    return g;
+}
 
-    // per-thread maximum of |x| (fmaxf drops NaN operands)
-    float gm = 0.0f;
-    for (unsigned i = tid; i < f4; i += NT) gm = fmaxf(gm, abs4max(row4[i]));
-    const unsigned gb = __float_as_uint(gm);
-
-    // round 1: exponent byte of the per-thread maxima
+// Bound from a two-round histogram over the per-thread maxima: at least k threads, hence at least
+// k elements, reach the returned value.  All threads call it; contains __syncthreads().
+template <int NT>
+__device__ __forceinline__ float topk_bound_hist(unsigned gb, unsigned k, TopkScratch &s) {
+    const int tid = threadIdx.x;
     for (int i = tid; i < 256; i += NT) s.hist[i] = 0;
-    if (tid == 0) { s.count = 0; s.nwork = 0; }
     __syncthreads();
-    atomicAdd(&s.hist[gb >> 23], 1u);
+    atomicAdd(&s.hist[gb >> 23], 1u);                      // round 1: exponent byte
     __syncthreads();
     if (tid < 32) hist_select_warp(s, k);
     __syncthreads();
     const unsigned b1 = s.sel_bin, need1 = s.sel_need;
+    for (int i = tid; i < 256; i += NT) s.hist[i] = 0;     // warp 0 is done reading the histogram
     __syncthreads();
-    // round 2: next 8 bits among the maxima inside bin b1
-    for (int i = tid; i < 256; i += NT) s.hist[i] = 0;
-    __syncthreads();
-    if ((gb >> 23) == b1) atomicAdd(&s.hist[(gb >> 15) & 0xFFu], 1u);
+    if ((gb >> 23) == b1) atomicAdd(&s.hist[(gb >> 15) & 0xFFu], 1u);   // round 2: next 8 bits
     __syncthreads();
     if (tid < 32) hist_select_warp(s, need1);
     __syncthreads();
-    const float bound = __uint_as_float((b1 << 23) | (s.sel_bin << 15));
+    return __uint_as_float((b1 << 23) | (s.sel_bin << 15));
+}
 
-    // threads whose maximum reaches the bound own all candidates
-    if (gm >= bound) {
-        const unsigned pos = atomicAdd(&s.nwork, 1u);
-        s.worklist[pos] = (unsigned short)tid;
-    }
-    __syncthreads();
-    const unsigned per_thread = (f4 + NT - 1) / NT;
-    const unsigned items = s.nwork * per_thread;
-    for (unsigned item = tid; item < items; item += NT) {
-        const unsigned entry = item / per_thread, f = item - entry * per_thread;
-        const unsigned i = (unsigned)s.worklist[entry] + f * NT;
-        if (i < f4) {
+// Append every element with |x| >= bound to s.cand (count in s.count, which the caller zeroed
+// behind a barrier).  Only float4s whose maximum m4[f] reaches the bound are read again.
+template <int NT, int IT>
+__device__ __forceinline__ void topk_collect(const float *row, unsigned cols, const unsigned (&m4)[IT],
+                                             float bound, TopkScratch &s) {
+    const unsigned f4 = cols >> 2;
+    const float4 *row4 = reinterpret_cast<const float4 *>(row);
+    const unsigned bb = __float_as_uint(bound);
+#pragma unroll
+    for (int f = 0; f < IT; ++f) {
+        const unsigned i = f * NT + threadIdx.x;
+        if (m4[f] >= bb && i < f4) {
             const float4 a = row4[i];
             const float v[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
@@ -240,14 +261,94 @@ __device__ void topk_row(float *row, unsigned cols, unsigned k, TopkScratch &s, 
             }
         }
     }
-    __syncthreads();
-    const unsigned count = s.count;
-    if (count > kCandCap || count < k) {          // ties / zeros: take the exact path
-        topk_exact<NT>(row, cols, k, s, out_idx, out_val, zero_selected);
-        return;
+}
+
+// Rank the `count` candidates by counting (composites are distinct), emit those of rank < k and,
+// with zero_selected, zero them in the row.  P = 64, 128 or 256 >= count; NT / P threads share the
+// comparisons of one candidate.  Leaves |x| of the k-th entry in s.kth_bits.  All threads call it;
+// contains __syncthreads() and ends with one.
+template <int NT, int P>
+__device__ __forceinline__ void topk_rank_emit(float *row, unsigned count, unsigned k, TopkScratch &s, uint16_t *out_idx,
+                                               float *out_val, bool zero_selected) {
+    constexpr int PARTS = NT / P;
+    const int tid = threadIdx.x;
+    const unsigned j = tid % P, part = tid / P;
+    if (PARTS > 1 && tid < P) s.hist[tid] = 0;             // hist doubles as the rank accumulator
+    if (PARTS > 1) __syncthreads();
+    unsigned rank = 0;
+    const unsigned long long mine = j < count ? s.cand[j] : 0ull;
+    if (j < count && part < (unsigned)PARTS) {
+        for (unsigned i = part; i < count; i += PARTS) rank += s.cand[i] > mine ? 1u : 0u;
+        if (PARTS > 1) atomicAdd(&s.hist[j], rank);
     }
-    if (tid < 32) sort_emit_dispatch(s, row, count, k, out_idx, out_val, zero_selected);
+    if (PARTS > 1) {
+        __syncthreads();
+        rank = s.hist[j];
+    }
+    if (tid < P && j < count && rank < k) {
+        const unsigned col = 0xFFFFu - (unsigned)(mine & 0xFFFFull);
+        const float v = row[col];
+        out_idx[rank] = (uint16_t)col;
+        out_val[rank] = v;
+        if (rank == k - 1) s.kth_bits = __float_as_uint(v) & 0x7fffffffu;
+        if (zero_selected) {
+            row[col] = 0.0f;
+            atomicOr(&s.dirty[col >> 7], 1u << ((col >> 2) & 31u));
+        }
+    }
     __syncthreads();
+}
+
+// Fast path with fallback.  `row` is a shared-memory row of `cols` floats, cols % 4 == 0,
+// cols <= 4 * NT * IT, 16-byte aligned; k <= min(kCandCap, NT).  `gb` / `m4` come from
+// row_thread_max(); `special` (uniform over the CTA) says that some thread saw Inf or NaN, which
+// sends the row down the exact path.  `hint` (uniform) is a guess of the bound, normally a little
+// below the k-th largest |x| of the row this CTA handled before (0 = no guess): any bound that
+// at least k and at most kCandCap elements reach gives the exact answer, so a wrong guess only
+// costs the histogram search.  Returns the guess for the next row.  All threads call it; the
+// caller must have executed a __syncthreads() since the row was last written; ends with one.
+template <int NT, int IT>
+__device__ float topk_row(float *row, unsigned cols, unsigned k, TopkScratch &s, uint16_t *out_idx, float *out_val,
+                          bool zero_selected, unsigned gb, const unsigned (&m4)[IT], bool special, float hint) {
+    const int tid = threadIdx.x;
+    for (int i = tid; i < 256; i += NT) s.dirty[i] = 0;
+    if (tid == 0) s.count = 0;
+    __syncthreads();
+    if (special) {
+        topk_exact<NT>(row, cols, k, s, out_idx, out_val, zero_selected);
+        return 0.0f;
+    }
+    BSQ_TT(0);
+    unsigned count = 0;
+    bool have = false;
+    if (hint > 0.0f) {
+        topk_collect<NT, IT>(row, cols, m4, hint, s);
+        __syncthreads();
+        count = s.count;
+        have = count >= k && count <= (unsigned)kCandCap;
+        if (!have) {
+            __syncthreads();
+            if (tid == 0) s.count = 0;
+        }
+    }
+    BSQ_TT(1);
+    if (!have) {
+        const float bound = topk_bound_hist<NT>(gb, k, s);          // its barriers also publish count = 0
+        topk_collect<NT, IT>(row, cols, m4, bound, s);
+        __syncthreads();
+        count = s.count;
+        if (count > (unsigned)kCandCap || count < k) {                // ties / zeros: exact path
+            topk_exact<NT>(row, cols, k, s, out_idx, out_val, zero_selected);
+            return 0.0f;
+        }
+    }
+    BSQ_TT(2);
+    if (count <= 64) topk_rank_emit<NT, 64>(row, count, k, s, out_idx, out_val, zero_selected);
+    else if (count <= 128) topk_rank_emit<NT, 128>(row, count, k, s, out_idx, out_val, zero_selected);
+    else topk_rank_emit<NT, 256>(row, count, k, s, out_idx, out_val, zero_selected);
+    BSQ_TT(3);
+    // next guess: 7/8 of this row's k-th largest magnitude
+    return __uint_as_float(s.kth_bits) * 0.875f;
 }
 
 }  // namespace bsq
