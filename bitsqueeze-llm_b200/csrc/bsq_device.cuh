@@ -164,6 +164,15 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, unsigned parity
     return false;
 }
 
+// CTA-wide wait for a bulk copy: only warp 0 polls the barrier (a polling warp burns issue slots
+// whether 1 or 32 of its lanes spin), everybody else parks at the CTA barrier.  Returns false, for
+// all threads alike, if the wait gave up.
+__device__ __forceinline__ bool cta_wait_copy(uint64_t *bar, unsigned parity, unsigned *status) {
+    bool ok = true;
+    if (threadIdx.x < 32) ok = mbar_wait_bounded(bar, parity, status);
+    return __syncthreads_and(ok) != 0;
+}
+
 // Order generic-proxy accesses to shared memory before later async-proxy (bulk copy) ones.
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -182,7 +182,7 @@ __global__ void __launch_bounds__(NT, 1536 / NT)
             mbar_expect_tx(&bar, bytes);
             bulk_g2s(row, in + (size_t)r * cols, bytes, &bar);
         }
-        if (!mbar_wait_bounded(&bar, phase, status)) return;
+        if (!cta_wait_copy(&bar, phase, status)) return;
         phase ^= 1u;
         BSQ_T(0, 1);
         unsigned m4[IT];
@@ -271,7 +271,7 @@ __global__ void __launch_bounds__(NT, 2048 / NT)
         row_block_scales<NT, true>(cols, dq, absmax_scratch + (size_t)r * blocks_per_row, blk, nullptr,
                                    scale_codes + (size_t)r * blocks_per_row);
         BSQ_T(1, 1);
-        if (!mbar_wait_bounded(&bar, phase, status)) return;
+        if (!cta_wait_copy(&bar, phase, status)) return;
         phase ^= 1u;
         BSQ_T(1, 2);
         for (unsigned j = tid; j < k; j += NT) {

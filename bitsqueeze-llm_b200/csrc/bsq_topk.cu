@@ -41,7 +41,7 @@ __global__ void __launch_bounds__(NT, 1536 / NT)
             mbar_expect_tx(&bar, bytes);
             bulk_g2s(row, in + (size_t)r * cols, bytes, &bar);
         }
-        if (!mbar_wait_bounded(&bar, phase, status)) return;
+        if (!cta_wait_copy(&bar, phase, status)) return;
         phase ^= 1u;
         unsigned m4[IT];
         const unsigned gb = row_thread_max<NT, IT>(row, cols, m4);
