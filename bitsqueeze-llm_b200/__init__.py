@@ -70,6 +70,8 @@ SIGNATURES = {
     "bsq_nf4_quantize": (_i, [_vp, _u64, _vp, _vp, _vp, _vp]),
     "bsq_nf4dq_scratch_bytes": (_sz, [_u64]),
     "bsq_nf4dq_quantize": (_i, [_vp, _u64, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "bsq_nf4dq_quantize_static_max_elements": (_u64, []),
+    "bsq_nf4dq_quantize_static": (_i, [_vp, _u64, _vp, _vp, _vp, _vp]),
     "bsq_nf4_dequantize": (_i, [_vp, _vp, _u64, _vp, _vp]),
     "bsq_nf4dq_dequantize": (_i, [_vp, _vp, _vp, _u64, _vp, _vp]),
     "bsq_frontend_supported": (_i, [_u32, _u32, _u32]),

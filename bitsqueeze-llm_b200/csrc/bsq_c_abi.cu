@@ -66,6 +66,13 @@ int bsq_nf4dq_quantize(const float *d_x, uint64_t n, float *d_dq, uint8_t *d_sca
     if (!d_x || !n || !d_dq || !d_scale_codes || !d_data || !d_scratch) return 1;
     return rc(nf4dq_quantize(d_x, n, d_dq, d_scale_codes, d_data, d_deq_out, d_scratch, device_sm_count(), as_stream(stream)));
 }
+uint64_t bsq_nf4dq_quantize_static_max_elements(void) { return nf4dq_static_max_elements(); }
+int bsq_nf4dq_quantize_static(const float *d_x, uint64_t n, float *d_dq, uint8_t *d_scale_codes, uint8_t *d_data,
+                              void *stream) {
+    if (!d_x || !d_dq || !d_scale_codes || !d_data) return 1;
+    if (n == 0 || n > nf4dq_static_max_elements()) return 1;      // beyond the built-in scratch: use bsq_nf4dq_quantize
+    return rc(nf4dq_quantize_static(d_x, n, d_dq, d_scale_codes, d_data, device_sm_count(), as_stream(stream)));
+}
 int bsq_nf4_dequantize(const float *d_scales, const uint8_t *d_data, uint64_t n, float *d_out, void *stream) {
     if (!d_scales || !d_data || !n || !d_out) return 1;
     return rc(nf4_dequantize(d_scales, d_data, n, d_out, device_sm_count(), as_stream(stream)));

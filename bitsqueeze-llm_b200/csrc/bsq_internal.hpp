@@ -17,6 +17,10 @@ cudaError_t nf4_quantize(const float *d_x, uint64_t n, float *d_scales, uint8_t 
 size_t nf4dq_scratch_bytes(uint64_t n);
 cudaError_t nf4dq_quantize(const float *d_x, uint64_t n, float *d_dq, uint8_t *d_scale_codes, uint8_t *d_data,
                            float *d_deq_out, void *d_scratch, int sm_count, cudaStream_t stream);
+// Variant for callers that must not allocate: scratch is a fixed array inside the library.
+uint64_t nf4dq_static_max_elements();
+cudaError_t nf4dq_quantize_static(const float *d_x, uint64_t n, float *d_dq, uint8_t *d_scale_codes, uint8_t *d_data,
+                                  int sm_count, cudaStream_t stream);
 cudaError_t nf4_dequantize(const float *d_scales, const uint8_t *d_data, uint64_t n, float *d_out, int sm_count,
                            cudaStream_t stream);
 cudaError_t nf4dq_dequantize(const float *d_dq, const uint8_t *d_scale_codes, const uint8_t *d_data, uint64_t n,

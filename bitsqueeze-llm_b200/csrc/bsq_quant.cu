@@ -14,8 +14,16 @@
 #include "bsq_device.cuh"
 #include "bsq_internal.hpp"
 
+#include <mutex>
+
 namespace bsq {
 namespace {
+
+// Scratch of nf4dq_quantize_static(): global-max word (16 bytes) + one float per 64-element
+// block, for at most kStaticMaxElems elements.  Lives in the module image of every device that
+// loads the library, from load to exit.
+constexpr uint64_t kStaticMaxElems = 1ull << 24;
+static __device__ __align__(256) unsigned char g_static_scratch[16 + (kStaticMaxElems / 64) * sizeof(float)];
 
 constexpr int kBatch = 1024;
 constexpr int kThreads = 256;
@@ -290,6 +298,37 @@ cudaError_t nf4dq_quantize(const float *d_x, uint64_t n, float *d_dq, uint8_t *d
         encode_flat_kernel<true, false><<<grid, kThreads, 0, stream>>>(d_x, n, vec, absmax, gmax, nullptr, d_scale_codes,
                                                                          d_dq, d_data, nullptr);
     return cudaGetLastError();
+}
+
+uint64_t nf4dq_static_max_elements() { return kStaticMaxElems; }
+
+// NF4_DQ quantiser that allocates nothing: its scratch is the file-scope array above.  The device
+// address of that array is looked up once per device (cudaGetSymbolAddress, with that device
+// current) the first time the function runs there; that first call should therefore come before
+// any stream capture.  All calls on a device share the array: work from two calls that overlaps
+// on the GPU (different streams) races on it.  Stale contents are harmless: the global-max word is
+// cleared at the start of every call and every block maximum that is read was written by the same call.
+cudaError_t nf4dq_quantize_static(const float *d_x, uint64_t n, float *d_dq, uint8_t *d_scale_codes, uint8_t *d_data,
+                                  int sm_count, cudaStream_t stream) {
+    static std::mutex mu;
+    static void *scratch_of_device[64] = {};
+    if (n == 0 || n > kStaticMaxElems) return cudaErrorInvalidValue;
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    void *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> g(mu);
+        if (!scratch_of_device[dev]) {
+            void *p = nullptr;
+            err = cudaGetSymbolAddress(&p, g_static_scratch);     // host code must not pass the symbol itself
+            if (err != cudaSuccess) return err;
+            scratch_of_device[dev] = p;
+        }
+        scratch = scratch_of_device[dev];
+    }
+    return nf4dq_quantize(d_x, n, d_dq, d_scale_codes, d_data, nullptr, scratch, sm_count, stream);
 }
 
 cudaError_t nf4_dequantize(const float *d_scales, const uint8_t *d_data, uint64_t n, float *d_out, int sm_count,

@@ -74,6 +74,19 @@ size_t bsq_nf4dq_scratch_bytes(uint64_t n);
 /* quantization_cuda_compress with an NF4_DQ array.  d_dq: 1 float, d_scale_codes: ceil(n/64) bytes. */
 int bsq_nf4dq_quantize(const float *d_x, uint64_t n, float *d_dq, uint8_t *d_scale_codes, uint8_t *d_data,
                        float *d_deq_out, void *d_scratch, void *stream);
+/* NF4_DQ quantiser for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference (there every quantiser context owns cudaMalloc'ed scratch).  Some callers hold a fixed
+ * memory budget carved out at start-up, or run where an allocation would stall or break them
+ * (inside a serving loop that must not touch the allocator, under a memory pool that owns the whole
+ * device); this entry point needs only the caller's input and output buffers.  Its scratch (one
+ * float per 64-element block) is a fixed array inside the library, so n is limited to
+ * bsq_nf4dq_quantize_static_max_elements() (2^24 elements, 1 MiB of scratch per device); larger n
+ * returns 1.  The first call on a device looks up the array's device address and should happen
+ * outside stream capture.  All calls on a device share the array: do not let two of them overlap
+ * on the GPU.  Results are identical to bsq_nf4dq_quantize. */
+uint64_t bsq_nf4dq_quantize_static_max_elements(void);
+int bsq_nf4dq_quantize_static(const float *d_x, uint64_t n, float *d_dq, uint8_t *d_scale_codes, uint8_t *d_data,
+                              void *stream);
 /* quantization_cuda_decompress, quantization_cuda.cuh:91-94 */
 int bsq_nf4_dequantize(const float *d_scales, const uint8_t *d_data, uint64_t n, float *d_out, void *stream);
 int bsq_nf4dq_dequantize(const float *d_dq, const uint8_t *d_scale_codes, const uint8_t *d_data, uint64_t n,
