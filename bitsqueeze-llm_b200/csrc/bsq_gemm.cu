@@ -1,0 +1,232 @@
+// FP32 GEMM building block of the low-rank stages (sm_100a).
+//
+// Replaces the cublasSgemm / cublasSdgmm call sites of the reference
+// (modules/svd_lowrank_cuda/src/svd_lowrank_cuda.cu:293-309,319-335,344-360,370-386,409-425 and
+// modules/reconstruct_lowrank_cuda/src/reconstruct_lowrank_cuda.cu:31-61) with one kernel that reads
+// the caller's row-major matrices in whichever orientation a product needs, so the reference's
+// explicit transposes of the input and of U, V (svd_lowrank_cuda_utils.cuh:91-109) disappear:
+//
+//   C[M x N] = opA[M x K] * opB[K x N]
+//   A_KMAJOR  : opA(i, kk) = A[i * lda + kk]   (A used as stored)      else opA(i, kk) = A[kk * lda + i]  (A^T)
+//   B_KMAJOR  : opB(kk, j) = B[j * ldb + kk]   (B^T of a row-major B)  else opB(kk, j) = B[kk * ldb + j]
+//
+// All the products of the randomized SVD are "skinny": one of M, N is the rank k (<= 256), the other
+// one matrix dimension, and K is the other matrix dimension, so there are few output tiles; the grid's
+// third dimension splits K and a second kernel adds the partial tiles in a fixed order (deterministic).
+// Optional fusions: a per-k scale on opA (U * diag(S) of reconstruct), and in the epilogue
+// "minuend - C" with an any(|.| > FLT_EPSILON) flag (the reference's subtract_kernel + has_nonzero_kernel,
+// src/bitsqz_llm.cu:164-184).
+//
+// This version computes on the FP32 pipes (128 x 128 x 16 tiles, 8 x 8 per thread, double-buffered
+// shared memory).
+#include "bsq_internal.hpp"
+
+namespace bsq {
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 16, GT = 256;
+constexpr int PAD = 4;
+
+struct GemmArgs {
+    const float *A, *B;
+    float *C;                  // output, or partial tiles when splits > 1
+    int M, N, K;
+    long lda, ldb, ldc;
+    const float *kscale;       // nullable: opA(i, kk) *= kscale[kk]
+    int splits;                // K splits (grid.z)
+    int k_per_split;           // multiple of BK
+    long split_stride;         // elements between partial results
+    const float *minuend;      // nullable (only without splits): C = minuend - acc
+    long ldm;
+    unsigned *flag;            // nullable: |= 1 when some |C| > FLT_EPSILON (with minuend)
+};
+
+template <bool KMAJOR>
+__device__ __forceinline__ void load_tile(const float *__restrict__ P, long ld, int rows_total, int k_total, int row0, int k0,
+                                          int k_end, float (*S)[BM + PAD], bool vec_ok, const float *kscale) {
+    // fills S[kk][r] = op(row0 + r, k0 + kk) for r < 128, kk < 16 (zero outside the matrix / split)
+    const int t = threadIdx.x;
+    if (KMAJOR) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = (t >> 2) + h * 64, kk = (t & 3) * 4;
+            const int gr = row0 + r, gk = k0 + kk;
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (gr < rows_total) {
+                const float *src = P + (long)gr * ld + gk;
+                if (vec_ok && gk + 3 < k_end) {
+                    const float4 q = *reinterpret_cast<const float4 *>(src);
+                    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (gk + j < k_end) v[j] = src[j];
+                }
+                if (kscale) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (gk + j < k_end) v[j] = __fmul_rn(v[j], kscale[gk + j]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) S[kk + j][r] = v[j];
+        }
+    } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int kk = (t >> 5) + h * 8, r = (t & 31) * 4;
+            const int gk = k0 + kk, gr = row0 + r;
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (gk < k_end) {
+                const float *src = P + (long)gk * ld + gr;
+                if (vec_ok && gr + 3 < rows_total) {
+                    const float4 q = *reinterpret_cast<const float4 *>(src);
+                    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (gr + j < rows_total) v[j] = src[j];
+                }
+                if (kscale) {
+                    const float s = kscale[gk];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[j] = __fmul_rn(v[j], s);
+                }
+            }
+            *reinterpret_cast<float4 *>(&S[kk][r]) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+    }
+    (void)k_total;
+}
+
+template <bool A_KMAJOR, bool B_KMAJOR>
+__global__ void __launch_bounds__(GT) gemm_kernel(GemmArgs g) {
+    __shared__ __align__(16) float As[2][BK][BM + PAD];
+    __shared__ __align__(16) float Bs[2][BK][BN + PAD];
+    const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int k_begin = blockIdx.z * g.k_per_split;
+    const int k_end = min(g.K, k_begin + g.k_per_split);
+    const bool a_vec = (reinterpret_cast<uintptr_t>(g.A) % 16 == 0) && (g.lda % 4 == 0);
+    const bool b_vec = (reinterpret_cast<uintptr_t>(g.B) % 16 == 0) && (g.ldb % 4 == 0);
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+
+    int buf = 0;
+    if (k_begin < k_end) {
+        load_tile<A_KMAJOR>(g.A, g.lda, g.M, g.K, m0, k_begin, k_end, As[0], a_vec, g.kscale);
+        load_tile<B_KMAJOR>(g.B, g.ldb, g.N, g.K, n0, k_begin, k_end, Bs[0], b_vec, nullptr);
+    }
+    __syncthreads();
+    for (int k0 = k_begin; k0 < k_end; k0 += BK) {
+        if (k0 + BK < k_end) {
+            load_tile<A_KMAJOR>(g.A, g.lda, g.M, g.K, m0, k0 + BK, k_end, As[buf ^ 1], a_vec, g.kscale);
+            load_tile<B_KMAJOR>(g.B, g.ldb, g.N, g.K, n0, k0 + BK, k_end, Bs[buf ^ 1], b_vec, nullptr);
+        }
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            const float4 a0 = *reinterpret_cast<const float4 *>(&As[buf][kk][ty * 4]);
+            const float4 a1 = *reinterpret_cast<const float4 *>(&As[buf][kk][64 + ty * 4]);
+            const float4 b0 = *reinterpret_cast<const float4 *>(&Bs[buf][kk][tx * 4]);
+            const float4 b1 = *reinterpret_cast<const float4 *>(&Bs[buf][kk][64 + tx * 4]);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+        buf ^= 1;
+    }
+
+    float *C = g.C + (long)blockIdx.z * g.split_stride;
+    bool any = false;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int gm = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+        if (gm >= g.M) continue;
+#pragma unroll
+        for (int jh = 0; jh < 2; ++jh) {
+            const int gn = n0 + jh * 64 + tx * 4;
+            float v[4] = {acc[i][jh * 4 + 0], acc[i][jh * 4 + 1], acc[i][jh * 4 + 2], acc[i][jh * 4 + 3]};
+            if (g.minuend) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (gn + j < g.N) {
+                        v[j] = __fsub_rn(g.minuend[(long)gm * g.ldm + gn + j], v[j]);
+                        any |= fabsf(v[j]) > 1.1920928955078125e-07f;
+                    }
+            }
+            float *dst = C + (long)gm * g.ldc + gn;
+            if (gn + 3 < g.N && (reinterpret_cast<uintptr_t>(dst) % 16 == 0)) {
+                *reinterpret_cast<float4 *>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (gn + j < g.N) dst[j] = v[j];
+            }
+        }
+    }
+    if (g.flag && __any_sync(0xffffffffu, any) && (t & 31) == 0) atomicOr(g.flag, 1u);
+}
+
+// C = sum over splits of the partial results, in split order.
+__global__ void reduce_splits_kernel(const float *__restrict__ part, float *__restrict__ C, int M, int N, long ldc,
+                                     int splits, long split_stride) {
+    const long total = (long)M * N;
+    for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) {
+        const int i = (int)(e / N), j = (int)(e % N);
+        float s = 0.0f;
+        for (int z = 0; z < splits; ++z) s += part[z * split_stride + (long)i * N + j];
+        C[(long)i * ldc + j] = s;
+    }
+}
+
+}  // namespace
+
+size_t gemm_workspace_bytes(int M, int N, int max_splits) { return (size_t)M * N * max_splits * sizeof(float); }
+
+// Picks the K split so that about two CTAs per SM are busy; partials go to `workspace` (may be null: no split).
+cudaError_t gemm(bool a_kmajor, bool b_kmajor, const float *A, long lda, const float *B, long ldb, float *C, long ldc, int M,
+                 int N, int K, const float *kscale, const float *minuend, long ldm, unsigned *flag, float *workspace,
+                 size_t workspace_bytes, int sm_count, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
+    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    int splits = 1;
+    if (workspace && !minuend && tiles < 2 * sm_count) {
+        splits = (2 * sm_count + tiles - 1) / tiles;
+        const int max_by_k = (K + 4 * BK - 1) / (4 * BK);                      // at least 64 of K per split
+        const int max_by_ws = (int)(workspace_bytes / ((size_t)M * N * sizeof(float)));
+        splits = max(1, min(splits, min(max_by_k, max_by_ws)));
+    }
+    GemmArgs g{};
+    g.A = A; g.B = B; g.M = M; g.N = N; g.K = K; g.lda = lda; g.ldb = ldb;
+    g.kscale = kscale;
+    g.splits = splits;
+    g.k_per_split = ((K + splits - 1) / splits + BK - 1) / BK * BK;
+    g.minuend = minuend; g.ldm = ldm; g.flag = minuend ? flag : nullptr;
+    if (splits > 1) {
+        g.C = workspace; g.ldc = N; g.split_stride = (long)M * N;
+    } else {
+        g.C = C; g.ldc = ldc; g.split_stride = 0;
+    }
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, splits);
+    if (a_kmajor && b_kmajor) gemm_kernel<true, true><<<grid, GT, 0, stream>>>(g);
+    else if (a_kmajor) gemm_kernel<true, false><<<grid, GT, 0, stream>>>(g);
+    else if (b_kmajor) gemm_kernel<false, true><<<grid, GT, 0, stream>>>(g);
+    else gemm_kernel<false, false><<<grid, GT, 0, stream>>>(g);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess || splits == 1) return err;
+    const long total = (long)M * N;
+    long rg = (total + 255) / 256;
+    if (rg > (long)sm_count * 8) rg = (long)sm_count * 8;
+    const int rgrid = (int)rg;
+    reduce_splits_kernel<<<rgrid, 256, 0, stream>>>(workspace, C, M, N, ldc, splits, (long)M * N);
+    return cudaGetLastError();
+}
+
+}  // namespace bsq

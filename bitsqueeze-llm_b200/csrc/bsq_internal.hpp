@@ -66,6 +66,13 @@ bool topk_rows_fit_smem(const void *d_in, const void *d_residual, uint32_t cols,
 // Replaces svd_lowrank_cuda_initialize / svd_lowrank_cuda / svd_lowrank_cuda_release
 // (modules/svd_lowrank_cuda/src/svd_lowrank_cuda.cu:541-581) and reconstruct_lowrank_cuda
 // (modules/reconstruct_lowrank_cuda/src/reconstruct_lowrank_cuda.cu:153-171).
+// C[M x N] = opA[M x K] * opB[K x N] in FP32 (bsq_gemm.cu).  a_kmajor: opA(i,kk) = A[i*lda+kk], else A[kk*lda+i];
+// b_kmajor: opB(kk,j) = B[j*ldb+kk], else B[kk*ldb+j].  kscale (nullable) scales opA along K.  minuend (nullable):
+// C = minuend - product, *flag |= 1 when some |C| > FLT_EPSILON.  workspace (nullable) enables a deterministic K split.
+cudaError_t gemm(bool a_kmajor, bool b_kmajor, const float *A, long lda, const float *B, long ldb, float *C, long ldc, int M,
+                 int N, int K, const float *kscale, const float *minuend, long ldm, unsigned *flag, float *workspace,
+                 size_t workspace_bytes, int sm_count, cudaStream_t stream);
+
 struct SvdWorkspace;
 SvdWorkspace *svd_workspace_create(int m, int n, int k, int niter, int sm_count);
 void svd_workspace_destroy(SvdWorkspace *ws);

@@ -1,8 +1,225 @@
-// placeholder until the low-rank stages land
+// Randomized low-rank SVD and low-rank reconstruction (sm_100a host driver + glue kernels).
+//
+// Replaces svd_lowrank_cuda_initialize / svd_lowrank_cuda / svd_lowrank_cuda_release
+// (modules/svd_lowrank_cuda/src/svd_lowrank_cuda.cu:284-581) and reconstruct_lowrank_cuda
+// (modules/reconstruct_lowrank_cuda/src/reconstruct_lowrank_cuda.cu:21-62).
+//
+// Same algorithm family as the reference (Halko-style range finder: Y = W Omega, niter power
+// iterations with re-orthonormalisation, projection B = Q^T W, small SVD, U = Q U_hat; the working
+// matrix W is A, or A^T when A has fewer rows than columns), different linear algebra:
+//   * every product with the big matrix reads the caller's row-major A directly, in either
+//     orientation (bsq_gemm.cu) -- no transposed copy of A, no transposes of U and V on the way out;
+//   * tall panels are orthonormalised through their k x k Gram matrix instead of Householder QR:
+//     G = Y^T Y = V L V^T, Y <- Y V L^(-1/2), applied twice.  Eigenvalues are clamped from below at
+//     eps * max(L), so rank-deficient panels (exactly low-rank inputs, all-zero inputs) only leave
+//     some columns shorter than unit length instead of dividing by zero;
+//   * the small SVD works on a k x k core: B^T = Q2 C with C the product of the two inverse
+//     transforms, C = Uc S Vc^T, V_hat = Q2 Uc, U = Q Vc.
+// The two k x k factorisations (symmetric eigenproblem, SVD of C) are cuSOLVER calls for now
+// (syevd, gesvdj); everything that touches an M- or N-sized array is a kernel of this library.
+// Omega comes from cuRAND's XORWOW generator like the reference's (svd_lowrank_cuda.cu:143,289-291),
+// seeded per call, column-major N x k.
 #include "bsq_internal.hpp"
+
+#include <curand.h>
+#include <cusolverDn.h>
+
+#include <algorithm>
+#include <new>
+
 namespace bsq {
-SvdWorkspace *svd_workspace_create(int, int, int, int, int) { return nullptr; }
-void svd_workspace_destroy(SvdWorkspace *) {}
-cudaError_t svd_lowrank(SvdWorkspace *, const float *, float *, float *, float *, unsigned long long, unsigned *, cudaStream_t) { return cudaErrorNotSupported; }
-cudaError_t reconstruct_lowrank(const float *, const float *, const float *, int, int, int, const float *, float *, unsigned *, int, cudaStream_t) { return cudaErrorNotSupported; }
+
+struct SvdWorkspace {
+    int m = 0, n = 0, k = 0, niter = 0, sm_count = 148;
+    bool transposed = false;            // working matrix is A^T
+    int M = 0, N = 0;                   // working dimensions, M >= N
+    float *omega = nullptr;             // N x k, column-major
+    float *y = nullptr, *y2 = nullptr;  // M x k
+    float *z = nullptr, *z2 = nullptr;  // N x k
+    float *g = nullptr;                 // k x k Gram / eigenvectors
+    float *w = nullptr;                 // k eigenvalues
+    float *t = nullptr, *tinv1 = nullptr, *tinv2 = nullptr, *core = nullptr;   // k x k
+    float *uc = nullptr, *vc = nullptr; // k x k outputs of the core SVD
+    float *gemm_ws = nullptr;
+    size_t gemm_ws_bytes = 0;
+    float *solver_work = nullptr;
+    int lwork = 0;
+    int *dev_info = nullptr;
+    curandGenerator_t rng = nullptr;
+    cusolverDnHandle_t solver = nullptr;
+    gesvdjInfo_t svdj = nullptr;
+};
+
+namespace {
+
+// From eigenpairs (vec column-major, ascending lam) build T = V diag(c^-1) and, optionally,
+// Tinv = diag(c) V^T, both row-major; c_j = sqrt(max(lam_j, eps * lam_max)); an all-zero panel gives T = Tinv = 0.
+__global__ void build_transforms_kernel(const float *__restrict__ vec, const float *__restrict__ lam, int k,
+                                        float *__restrict__ T, float *__restrict__ Tinv) {
+    const float lmax = fmaxf(lam[k - 1], 0.0f);
+    const float floor_l = lmax * 1.1920928955078125e-07f;
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < k * k; e += gridDim.x * blockDim.x) {
+        const int i = e / k, j = e % k;
+        const float l = fmaxf(lam[j], floor_l);
+        const float c = l > 0.0f ? sqrtf(l) : 0.0f;           // 0: the whole panel is zero, drop the direction
+        const float v = vec[(size_t)j * k + i];               // V(i, j)
+        T[(size_t)i * k + j] = c > 0.0f ? v / c : 0.0f;
+        if (Tinv) Tinv[(size_t)j * k + i] = c * v;
+    }
 }
+
+bool alloc_f(float **p, size_t count) {
+    if (cudaMalloc(reinterpret_cast<void **>(p), std::max<size_t>(count, 1) * sizeof(float)) != cudaSuccess) {
+        cudaGetLastError();
+        *p = nullptr;
+        return false;
+    }
+    return true;
+}
+
+// Y (rows x k, row-major) <- orthonormalised Y, two Gram passes.  `tmp` is a second rows x k buffer.
+// tinv_a / tinv_b (nullable) receive the inverse transforms of the two passes.
+cudaError_t orthonormalise(SvdWorkspace *ws, float *Y, float *tmp, int rows, float *tinv_a, float *tinv_b,
+                           cudaStream_t st) {
+    const int k = ws->k;
+    float *src = Y, *dst = tmp;
+    for (int pass = 0; pass < 2; ++pass) {
+        // G = src^T src
+        cudaError_t err = gemm(false, false, src, k, src, k, ws->g, k, k, k, rows, nullptr, nullptr, 0, nullptr, ws->gemm_ws,
+                               ws->gemm_ws_bytes, ws->sm_count, st);
+        if (err != cudaSuccess) return err;
+        if (cusolverDnSsyevd(ws->solver, CUSOLVER_EIG_MODE_VECTOR, CUBLAS_FILL_MODE_LOWER, k, ws->g, k, ws->w,
+                             ws->solver_work, ws->lwork, ws->dev_info) != CUSOLVER_STATUS_SUCCESS)
+            return cudaErrorUnknown;
+        build_transforms_kernel<<<std::min(64, (k * k + 255) / 256), 256, 0, st>>>(ws->g, ws->w, k, ws->t,
+                                                                                  pass == 0 ? tinv_a : tinv_b);
+        err = cudaGetLastError();
+        if (err != cudaSuccess) return err;
+        // dst = src T
+        err = gemm(true, false, src, k, ws->t, k, dst, k, rows, k, k, nullptr, nullptr, 0, nullptr, nullptr, 0, ws->sm_count, st);
+        if (err != cudaSuccess) return err;
+        std::swap(src, dst);
+    }
+    return cudaSuccess;      // two swaps: the result is back in Y
+}
+
+// C[rows_out x k] = W * X or W^T * X for the working matrix W of the workspace.
+// X is row-major unless x_colmajor (Omega).
+cudaError_t times_w(SvdWorkspace *ws, const float *A, bool w_transposed_product, const float *X, bool x_colmajor, float *C,
+                    cudaStream_t st) {
+    // W = A (not transposed) or A^T.  "W * X" contracts over W's columns, "W^T * X" over its rows.
+    const bool use_a_as_stored = (w_transposed_product == ws->transposed);   // W*X with W=A, or W^T*X with W=A^T
+    const int rows_out = w_transposed_product ? ws->N : ws->M;
+    const int contract = w_transposed_product ? ws->M : ws->N;
+    const long ldx = x_colmajor ? contract : ws->k;
+    return gemm(use_a_as_stored, x_colmajor, A, ws->n, X, ldx, C, ws->k, rows_out, ws->k, contract, nullptr, nullptr, 0,
+                nullptr, ws->gemm_ws, ws->gemm_ws_bytes, ws->sm_count, st);
+}
+
+}  // namespace
+
+SvdWorkspace *svd_workspace_create(int m, int n, int k, int niter, int sm_count) {
+    if (m <= 0 || n <= 0 || k <= 0 || niter < 0) return nullptr;
+    SvdWorkspace *ws = new (std::nothrow) SvdWorkspace();
+    if (!ws) return nullptr;
+    ws->m = m; ws->n = n; ws->niter = niter; ws->sm_count = sm_count;
+    ws->k = std::max(1, std::min(k, std::min(m, n)));
+    ws->transposed = m < n;
+    ws->M = ws->transposed ? n : m;
+    ws->N = ws->transposed ? m : n;
+    const size_t kk = (size_t)ws->k * ws->k;
+    bool ok = alloc_f(&ws->omega, (size_t)ws->N * ws->k + 2) && alloc_f(&ws->y, (size_t)ws->M * ws->k) &&
+              alloc_f(&ws->y2, (size_t)ws->M * ws->k) && alloc_f(&ws->z, (size_t)ws->N * ws->k) &&
+              alloc_f(&ws->z2, (size_t)ws->N * ws->k) && alloc_f(&ws->g, kk) && alloc_f(&ws->w, ws->k) &&
+              alloc_f(&ws->t, kk) && alloc_f(&ws->tinv1, kk) && alloc_f(&ws->tinv2, kk) && alloc_f(&ws->core, kk) &&
+              alloc_f(&ws->uc, kk) && alloc_f(&ws->vc, kk);
+    // split-K partials: up to 2 * SMs tiles' worth of the largest skinny product, and of the Gram matrix
+    ws->gemm_ws_bytes = std::max((size_t)ws->M * ws->k * 4, kk * 2 * (size_t)sm_count) * sizeof(float);
+    ok = ok && alloc_f(&ws->gemm_ws, ws->gemm_ws_bytes / sizeof(float));
+    ok = ok && cudaMalloc(reinterpret_cast<void **>(&ws->dev_info), sizeof(int)) == cudaSuccess;
+    ok = ok && curandCreateGenerator(&ws->rng, CURAND_RNG_PSEUDO_DEFAULT) == CURAND_STATUS_SUCCESS;
+    ok = ok && cusolverDnCreate(&ws->solver) == CUSOLVER_STATUS_SUCCESS;
+    ok = ok && cusolverDnCreateGesvdjInfo(&ws->svdj) == CUSOLVER_STATUS_SUCCESS;
+    if (ok) {
+        int l1 = 0, l2 = 0;
+        ok = cusolverDnSsyevd_bufferSize(ws->solver, CUSOLVER_EIG_MODE_VECTOR, CUBLAS_FILL_MODE_LOWER, ws->k, ws->g, ws->k,
+                                         ws->w, &l1) == CUSOLVER_STATUS_SUCCESS &&
+             cusolverDnSgesvdj_bufferSize(ws->solver, CUSOLVER_EIG_MODE_VECTOR, 0, ws->k, ws->k, ws->core, ws->k, ws->w,
+                                          ws->uc, ws->k, ws->vc, ws->k, &l2, ws->svdj) == CUSOLVER_STATUS_SUCCESS;
+        ws->lwork = std::max(1, std::max(l1, l2));
+        ok = ok && alloc_f(&ws->solver_work, (size_t)ws->lwork);
+    }
+    if (!ok) {
+        cudaGetLastError();
+        svd_workspace_destroy(ws);
+        return nullptr;
+    }
+    return ws;
+}
+
+void svd_workspace_destroy(SvdWorkspace *ws) {
+    if (!ws) return;
+    float *bufs[] = {ws->omega, ws->y, ws->y2, ws->z, ws->z2, ws->g, ws->w, ws->t, ws->tinv1, ws->tinv2,
+                     ws->core, ws->uc, ws->vc, ws->gemm_ws, ws->solver_work};
+    for (float *p : bufs)
+        if (p) cudaFree(p);
+    if (ws->dev_info) cudaFree(ws->dev_info);
+    if (ws->svdj) cusolverDnDestroyGesvdjInfo(ws->svdj);
+    if (ws->solver) cusolverDnDestroy(ws->solver);
+    if (ws->rng) curandDestroyGenerator(ws->rng);
+    cudaGetLastError();
+    delete ws;
+}
+
+cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d_S, float *d_V, unsigned long long seed,
+                        unsigned *d_status, cudaStream_t st) {
+    (void)d_status;
+    if (!ws || !d_A || !d_U || !d_S || !d_V) return cudaErrorInvalidValue;
+    const int k = ws->k;
+    if (curandSetStream(ws->rng, st) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
+    if (cusolverDnSetStream(ws->solver, st) != CUSOLVER_STATUS_SUCCESS) return cudaErrorUnknown;
+    if (curandSetPseudoRandomGeneratorSeed(ws->rng, seed) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
+    if (curandSetGeneratorOffset(ws->rng, 0ULL) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
+    size_t count = (size_t)ws->N * k;
+    count += count & 1;                                   // the normal generator wants an even count
+    if (curandGenerateNormal(ws->rng, ws->omega, count, 0.0f, 1.0f) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
+
+    cudaError_t err;
+    // Y = W Omega, Q = orth(Y)
+    if ((err = times_w(ws, d_A, false, ws->omega, true, ws->y, st)) != cudaSuccess) return err;
+    if ((err = orthonormalise(ws, ws->y, ws->y2, ws->M, nullptr, nullptr, st)) != cudaSuccess) return err;
+    for (int it = 0; it < ws->niter; ++it) {
+        if ((err = times_w(ws, d_A, true, ws->y, false, ws->z, st)) != cudaSuccess) return err;          // Z = W^T Q
+        if ((err = orthonormalise(ws, ws->z, ws->z2, ws->N, nullptr, nullptr, st)) != cudaSuccess) return err;
+        if ((err = times_w(ws, d_A, false, ws->z, false, ws->y, st)) != cudaSuccess) return err;         // Y = W Qz
+        if ((err = orthonormalise(ws, ws->y, ws->y2, ws->M, nullptr, nullptr, st)) != cudaSuccess) return err;
+    }
+    // B^T = W^T Q = Q2 C
+    if ((err = times_w(ws, d_A, true, ws->y, false, ws->z, st)) != cudaSuccess) return err;
+    if ((err = orthonormalise(ws, ws->z, ws->z2, ws->N, ws->tinv1, ws->tinv2, st)) != cudaSuccess) return err;
+    // C = Tinv2 Tinv1 (row-major k x k)
+    if ((err = gemm(true, false, ws->tinv2, k, ws->tinv1, k, ws->core, k, k, k, k, nullptr, nullptr, 0, nullptr, nullptr, 0,
+                    ws->sm_count, st)) != cudaSuccess)
+        return err;
+    // The row-major C read as column-major is C^T = Vc S Uc^T: the solver's "U" is Vc, its "V" is Uc.
+    if (cusolverDnSgesvdj(ws->solver, CUSOLVER_EIG_MODE_VECTOR, 0, k, k, ws->core, k, d_S, ws->vc, k, ws->uc, k,
+                          ws->solver_work, ws->lwork, ws->dev_info, ws->svdj) != CUSOLVER_STATUS_SUCCESS)
+        return cudaErrorUnknown;
+    // W = (Q Vc) S (Q2 Uc)^T; both k x k factors are column-major, i.e. K-major B operands
+    float *d_left = ws->transposed ? d_V : d_U;            // M x k factor
+    float *d_right = ws->transposed ? d_U : d_V;           // N x k factor
+    if ((err = gemm(true, true, ws->y, k, ws->vc, k, d_left, k, ws->M, k, k, nullptr, nullptr, 0, nullptr, nullptr, 0,
+                    ws->sm_count, st)) != cudaSuccess)
+        return err;
+    return gemm(true, true, ws->z, k, ws->uc, k, d_right, k, ws->N, k, k, nullptr, nullptr, 0, nullptr, nullptr, 0,
+                ws->sm_count, st);
+}
+
+cudaError_t reconstruct_lowrank(const float *d_U, const float *d_S, const float *d_V, int m, int n, int k,
+                                const float *d_minuend, float *d_out, unsigned *d_flag, int sm_count, cudaStream_t st) {
+    if (!d_U || !d_S || !d_V || !d_out || m <= 0 || n <= 0 || k <= 0) return cudaErrorInvalidValue;
+    // out(i, j) = sum_t (U(i, t) S(t)) V(j, t): A = U as stored with a per-k scale, B = V^T (K-major)
+    return gemm(true, true, d_U, k, d_V, k, d_out, n, m, n, k, d_S, d_minuend, n, d_flag, nullptr, 0, sm_count, st);
+}
+
+}  // namespace bsq
