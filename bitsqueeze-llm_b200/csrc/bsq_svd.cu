@@ -9,14 +9,15 @@
 // matrix W is A, or A^T when A has fewer rows than columns), different linear algebra:
 //   * every product with the big matrix reads the caller's row-major A directly, in either
 //     orientation (bsq_gemm.cu) -- no transposed copy of A, no transposes of U and V on the way out;
-//   * tall panels are orthonormalised through their k x k Gram matrix instead of Householder QR:
-//     G = Y^T Y = V L V^T, Y <- Y V L^(-1/2), applied twice.  Eigenvalues are clamped from below at
-//     eps * max(L), so rank-deficient panels (exactly low-rank inputs, all-zero inputs) only leave
-//     some columns shorter than unit length instead of dividing by zero;
-//   * the small SVD works on a k x k core: B^T = Q2 C with C the product of the two inverse
-//     transforms, C = Uc S Vc^T, V_hat = Q2 Uc, U = Q Vc.
-// The two k x k factorisations (symmetric eigenproblem, SVD of C) are cuSOLVER calls for now
-// (syevd, gesvdj); everything that touches an M- or N-sized array is a kernel of this library.
+//   * tall panels are orthonormalised through their k x k Gram matrix instead of Householder QR
+//     (Cholesky QR): G = Y^T Y = R^T R, Y <- Y R^-1 -- once inside the power iteration, twice for
+//     the bases that the result is built from.  G is shifted by 1e-5 max(diag G) before factoring,
+//     so rank-deficient panels (exactly low-rank inputs, all-zero inputs) only leave some columns
+//     shorter than unit length instead of dividing by zero;
+//   * the small SVD works on a k x k core: B^T = Q2 C with C = R2 R1 the product of the two
+//     triangular factors, C = Uc S Vc^T, V_hat = Q2 Uc, U = Q Vc.
+// The SVD of the k x k core is a cuSOLVER call for now (gesvdj); everything else, in particular
+// everything that touches an M- or N-sized array, is a kernel of this library.
 // Omega comes from cuRAND's XORWOW generator like the reference's (svd_lowrank_cuda.cu:143,289-291),
 // seeded per call, column-major N x k.
 #include "bsq_internal.hpp"
@@ -52,19 +53,68 @@ struct SvdWorkspace {
 
 namespace {
 
-// From eigenpairs (vec column-major, ascending lam) build T = V diag(c^-1) and, optionally,
-// Tinv = diag(c) V^T, both row-major; c_j = sqrt(max(lam_j, eps * lam_max)); an all-zero panel gives T = Tinv = 0.
-__global__ void build_transforms_kernel(const float *__restrict__ vec, const float *__restrict__ lam, int k,
-                                        float *__restrict__ T, float *__restrict__ Tinv) {
-    const float lmax = fmaxf(lam[k - 1], 0.0f);
-    const float floor_l = lmax * 1.1920928955078125e-07f;
-    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < k * k; e += gridDim.x * blockDim.x) {
-        const int i = e / k, j = e % k;
-        const float l = fmaxf(lam[j], floor_l);
-        const float c = l > 0.0f ? sqrtf(l) : 0.0f;           // 0: the whole panel is zero, drop the direction
-        const float v = vec[(size_t)j * k + i];               // V(i, j)
-        T[(size_t)i * k + j] = c > 0.0f ? v / c : 0.0f;
-        if (Tinv) Tinv[(size_t)j * k + i] = c * v;
+// One CTA factorises the shifted k x k Gram matrix G + s I = R^T R (Cholesky, R upper triangular, in
+// place over the upper triangle of A; s = 1e-5 max(diag G)) and inverts R.  The shift, and a floor of
+// s / 2 under every pivot, keep a rank-deficient panel from dividing by zero or taking the root of a
+// negative number: deficient directions just come out shorter than unit length (an all-zero panel
+// gives R = T = 0).  Any invertible R^-1 leaves the span of the panel unchanged; a second pass brings
+// every direction above ~3e-5 of the largest singular value to unit length.
+//   A    in: G (symmetric, row-major); out: R in the upper triangle, zeros below
+//   T    out: R^-1 (upper triangular, row-major), so that Y T has orthonormal columns
+//   Rcpy out (nullable): a copy of R, the inverse transform (Y = (Y T) R)
+__global__ void __launch_bounds__(1024) cholesky_inverse_kernel(float *A, int k, float *T, float *Rcpy) {
+    __shared__ float s_red[32];
+    __shared__ float s_floor, s_r;
+    const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
+    float md = 0.0f;
+    for (int i = tid; i < k; i += nt) md = fmaxf(md, A[(size_t)i * k + i]);
+    for (int d = 16; d > 0; d >>= 1) md = fmaxf(md, __shfl_xor_sync(0xffffffffu, md, d));
+    if (lane == 0) s_red[warp] = md;
+    __syncthreads();
+    if (tid == 0) {
+        float m = 0.0f;
+        for (int w = 0; w < nwarps; ++w) m = fmaxf(m, s_red[w]);
+        s_floor = m > 0.0f ? m * 1.0e-5f : 0.0f;
+    }
+    __syncthreads();
+    // shift: G + s I with s = 1e-5 max(diag G), far above the rounding noise of G, so that the Schur
+    // complements of a rank-deficient G stay diagonally dominant and R^-1 cannot blow up
+    for (int i = tid; i < k; i += nt) A[(size_t)i * k + i] += s_floor;
+    __syncthreads();
+    for (int j = 0; j < k; ++j) {
+        if (tid == 0) {
+            float d = A[(size_t)j * k + j];
+            if (!(d > 0.5f * s_floor)) d = 0.5f * s_floor;
+            s_r = d > 0.0f ? sqrtf(d) : 0.0f;
+            A[(size_t)j * k + j] = s_r;
+        }
+        __syncthreads();
+        const float inv = s_r > 0.0f ? 1.0f / s_r : 0.0f;
+        for (int c = j + 1 + tid; c < k; c += nt) A[(size_t)j * k + c] *= inv;        // row j of R
+        __syncthreads();
+        for (int i = j + 1 + warp; i < k; i += nwarps) {                               // trailing update
+            const float rji = A[(size_t)j * k + i];
+            for (int c = i + lane; c < k; c += 32) A[(size_t)i * k + c] -= rji * A[(size_t)j * k + c];
+        }
+        __syncthreads();
+    }
+    for (int e = tid; e < k * k; e += nt) {                // clear below the diagonal, copy R, clear T
+        const int i = e / k, c = e % k;
+        if (c < i) A[e] = 0.0f;
+        if (Rcpy) Rcpy[e] = c < i ? 0.0f : A[e];
+        T[e] = 0.0f;
+    }
+    __syncthreads();
+    // T = R^-1, row by row from the bottom: T(i,c) = (delta_ic - sum_{l=i+1..c} R(i,l) T(l,c)) / R(i,i)
+    for (int i = k - 1; i >= 0; --i) {
+        const float rii = A[(size_t)i * k + i];
+        const float inv = rii > 0.0f ? 1.0f / rii : 0.0f;
+        for (int c = i + tid; c < k; c += nt) {
+            float acc = (c == i) ? 1.0f : 0.0f;
+            for (int l = i + 1; l <= c; ++l) acc -= A[(size_t)i * k + l] * T[(size_t)l * k + c];
+            T[(size_t)i * k + c] = acc * inv;
+        }
+        __syncthreads();
     }
 }
 
@@ -77,22 +127,20 @@ bool alloc_f(float **p, size_t count) {
     return true;
 }
 
-// Y (rows x k, row-major) <- orthonormalised Y, two Gram passes.  `tmp` is a second rows x k buffer.
-// tinv_a / tinv_b (nullable) receive the inverse transforms of the two passes.
-cudaError_t orthonormalise(SvdWorkspace *ws, float *Y, float *tmp, int rows, float *tinv_a, float *tinv_b,
-                           cudaStream_t st) {
+// Y (rows x k, row-major) <- Y with orthonormalised columns, `passes` (1 or 2) Gram/Cholesky passes:
+// one is enough to keep a power iteration stable, two give orthonormality to rounding.  `tmp` is a
+// second rows x k buffer; the result ends in Y for 2 passes and in tmp for 1 (returned through *out).
+// r_a / r_b (nullable) receive the triangular factors of the passes (Y_in = Y_out * r_b * r_a).
+cudaError_t orthonormalise(SvdWorkspace *ws, float *Y, float *tmp, int rows, int passes, float *r_a, float *r_b,
+                           float **out, cudaStream_t st) {
     const int k = ws->k;
     float *src = Y, *dst = tmp;
-    for (int pass = 0; pass < 2; ++pass) {
+    for (int pass = 0; pass < passes; ++pass) {
         // G = src^T src
         cudaError_t err = gemm(false, false, src, k, src, k, ws->g, k, k, k, rows, nullptr, nullptr, 0, nullptr, ws->gemm_ws,
                                ws->gemm_ws_bytes, ws->sm_count, st);
         if (err != cudaSuccess) return err;
-        if (cusolverDnSsyevd(ws->solver, CUSOLVER_EIG_MODE_VECTOR, CUBLAS_FILL_MODE_LOWER, k, ws->g, k, ws->w,
-                             ws->solver_work, ws->lwork, ws->dev_info) != CUSOLVER_STATUS_SUCCESS)
-            return cudaErrorUnknown;
-        build_transforms_kernel<<<std::min(64, (k * k + 255) / 256), 256, 0, st>>>(ws->g, ws->w, k, ws->t,
-                                                                                  pass == 0 ? tinv_a : tinv_b);
+        cholesky_inverse_kernel<<<1, 1024, 0, st>>>(ws->g, k, ws->t, pass == 0 ? r_a : r_b);
         err = cudaGetLastError();
         if (err != cudaSuccess) return err;
         // dst = src T
@@ -100,7 +148,8 @@ cudaError_t orthonormalise(SvdWorkspace *ws, float *Y, float *tmp, int rows, flo
         if (err != cudaSuccess) return err;
         std::swap(src, dst);
     }
-    return cudaSuccess;      // two swaps: the result is back in Y
+    *out = src;
+    return cudaSuccess;
 }
 
 // C[rows_out x k] = W * X or W^T * X for the working matrix W of the workspace.
@@ -185,19 +234,25 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
     if (curandGenerateNormal(ws->rng, ws->omega, count, 0.0f, 1.0f) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
 
     cudaError_t err;
-    // Y = W Omega, Q = orth(Y)
+    float *q = nullptr, *qz = nullptr, *spare = nullptr;
+    // Y = W Omega, Q = orth(Y).  Panels ping-pong between the two buffers of their size.
     if ((err = times_w(ws, d_A, false, ws->omega, true, ws->y, st)) != cudaSuccess) return err;
-    if ((err = orthonormalise(ws, ws->y, ws->y2, ws->M, nullptr, nullptr, st)) != cudaSuccess) return err;
+    const int last_passes = 2;
+    if ((err = orthonormalise(ws, ws->y, ws->y2, ws->M, ws->niter == 0 ? last_passes : 1, nullptr, nullptr, &q, st)) != cudaSuccess)
+        return err;
     for (int it = 0; it < ws->niter; ++it) {
-        if ((err = times_w(ws, d_A, true, ws->y, false, ws->z, st)) != cudaSuccess) return err;          // Z = W^T Q
-        if ((err = orthonormalise(ws, ws->z, ws->z2, ws->N, nullptr, nullptr, st)) != cudaSuccess) return err;
-        if ((err = times_w(ws, d_A, false, ws->z, false, ws->y, st)) != cudaSuccess) return err;         // Y = W Qz
-        if ((err = orthonormalise(ws, ws->y, ws->y2, ws->M, nullptr, nullptr, st)) != cudaSuccess) return err;
+        if ((err = times_w(ws, d_A, true, q, false, ws->z, st)) != cudaSuccess) return err;               // Z = W^T Q
+        if ((err = orthonormalise(ws, ws->z, ws->z2, ws->N, 1, nullptr, nullptr, &qz, st)) != cudaSuccess) return err;
+        spare = (q == ws->y) ? ws->y2 : ws->y;
+        if ((err = times_w(ws, d_A, false, qz, false, spare, st)) != cudaSuccess) return err;             // Y = W Qz
+        float *other = (spare == ws->y) ? ws->y2 : ws->y;
+        if ((err = orthonormalise(ws, spare, other, ws->M, it + 1 == ws->niter ? last_passes : 1, nullptr, nullptr, &q, st)) !=
+            cudaSuccess)
+            return err;
     }
-    // B^T = W^T Q = Q2 C
-    if ((err = times_w(ws, d_A, true, ws->y, false, ws->z, st)) != cudaSuccess) return err;
-    if ((err = orthonormalise(ws, ws->z, ws->z2, ws->N, ws->tinv1, ws->tinv2, st)) != cudaSuccess) return err;
-    // C = Tinv2 Tinv1 (row-major k x k)
+    // B^T = W^T Q = Q2 C with C = R2 R1
+    if ((err = times_w(ws, d_A, true, q, false, ws->z, st)) != cudaSuccess) return err;
+    if ((err = orthonormalise(ws, ws->z, ws->z2, ws->N, 2, ws->tinv1, ws->tinv2, &qz, st)) != cudaSuccess) return err;
     if ((err = gemm(true, false, ws->tinv2, k, ws->tinv1, k, ws->core, k, k, k, k, nullptr, nullptr, 0, nullptr, nullptr, 0,
                     ws->sm_count, st)) != cudaSuccess)
         return err;
@@ -208,10 +263,10 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
     // W = (Q Vc) S (Q2 Uc)^T; both k x k factors are column-major, i.e. K-major B operands
     float *d_left = ws->transposed ? d_V : d_U;            // M x k factor
     float *d_right = ws->transposed ? d_U : d_V;           // N x k factor
-    if ((err = gemm(true, true, ws->y, k, ws->vc, k, d_left, k, ws->M, k, k, nullptr, nullptr, 0, nullptr, nullptr, 0,
+    if ((err = gemm(true, true, q, k, ws->vc, k, d_left, k, ws->M, k, k, nullptr, nullptr, 0, nullptr, nullptr, 0,
                     ws->sm_count, st)) != cudaSuccess)
         return err;
-    return gemm(true, true, ws->z, k, ws->uc, k, d_right, k, ws->N, k, k, nullptr, nullptr, 0, nullptr, nullptr, 0,
+    return gemm(true, true, qz, k, ws->uc, k, d_right, k, ws->N, k, k, nullptr, nullptr, 0, nullptr, nullptr, 0,
                 ws->sm_count, st);
 }
 
