@@ -11,6 +11,7 @@
 // selected entries zeroed -- are written back.  HBM-bound: 4 B read per element, 6k B written
 // per row (+ 4 B per element when the zeroed copy is wanted).
 #include "bsq_internal.hpp"
+#include "bsq_rowgroup.cuh"
 #include "bsq_topk.cuh"
 
 #include <math.h>
@@ -19,49 +20,48 @@ namespace bsq {
 namespace {
 
 // ---- rows that fit shared memory: cols % 4 == 0, k <= kCandCap, 16-byte aligned rows ----------
-template <int NT, int IT>
-__global__ void __launch_bounds__(NT, 1536 / NT)
-    topk_rows_smem_kernel(const float *__restrict__ in, float *residual, unsigned rows, unsigned cols, unsigned k,
-                          uint16_t *__restrict__ out_idx, float *__restrict__ out_val, unsigned *status) {
+// One group of G warps per row (bsq_rowgroup.cuh); a CTA holds several groups, rows are dealt out
+// round-robin over all groups of the grid.
+template <int G>
+__global__ void __launch_bounds__(512)
+    topk_rows_group_kernel(const float *__restrict__ in, float *residual, unsigned rows, unsigned cols, unsigned k,
+                           uint16_t *__restrict__ out_idx, float *__restrict__ out_val, unsigned *status, unsigned group_bytes,
+                           unsigned ctl_off) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    float *row = reinterpret_cast<float *>(smem_raw);
-    TopkScratch &s = *reinterpret_cast<TopkScratch *>(smem_raw + (size_t)cols * 4);
-    __shared__ __align__(8) uint64_t bar;
-    const int tid = threadIdx.x;
+    const RowGroup<G> g;
+    unsigned char *base = smem_raw + (size_t)g.gid * group_bytes;
+    float *row = reinterpret_cast<float *>(base);
+    GroupCtl &c = *reinterpret_cast<GroupCtl *>(base + ctl_off);
+    uint64_t *bar = reinterpret_cast<uint64_t *>(&c.bar);
     const unsigned bytes = cols * 4u;
-    if (tid == 0) {
-        mbar_init(&bar, 1);
+    const unsigned groups_per_cta = blockDim.x / RowGroup<G>::L;
+    if (g.lane == 0) {
+        mbar_init(bar, 1);
         mbar_fence_init();
     }
-    __syncthreads();
+    g.sync();
     unsigned phase = 0;
     float hint = 0.0f;
-    for (unsigned r = blockIdx.x; r < rows; r += gridDim.x) {
-        if (tid == 0) {
-            mbar_expect_tx(&bar, bytes);
-            bulk_g2s(row, in + (size_t)r * cols, bytes, &bar);
+    for (unsigned r = blockIdx.x * groups_per_cta + g.gid; r < rows; r += gridDim.x * groups_per_cta) {
+        if (g.lane == 0) {
+            mbar_expect_tx(bar, bytes);
+            bulk_g2s(row, in + (size_t)r * cols, bytes, bar);
         }
-        if (!cta_wait_copy(&bar, phase, status)) return;
+        if (!mbar_wait_bounded(bar, phase, status)) break;
         phase ^= 1u;
-        unsigned m4[IT];
-        const unsigned gb = row_thread_max<NT, IT>(row, cols, m4);
-        const bool special = __syncthreads_or(gb >= 0x7f800000u) != 0;
-        hint = topk_row<NT, IT>(row, cols, k, s, out_idx + (size_t)r * k, out_val + (size_t)r * k, residual != nullptr, gb, m4,
-                            special, hint);
-        if (residual != nullptr) {
-            fence_proxy_async_smem();
-            __syncthreads();
-            if (tid == 0) {
-                bulk_s2g(residual + (size_t)r * cols, row, bytes);
-                bulk_commit();
-                bulk_wait_read_all();
-            }
-        } else {
-            fence_proxy_async_smem();
+        bool special = false;
+        hint = group_topk_row<G>(g, c, row, cols, k, out_idx + (size_t)r * k, out_val + (size_t)r * k, residual != nullptr,
+                                 hint, &special);
+        fence_proxy_async_smem();
+        g.sync();
+        if (residual != nullptr && g.lane == 0) {
+            bulk_s2g(residual + (size_t)r * cols, row, bytes);
+            bulk_commit();
+            bulk_wait_read_all();
         }
-        __syncthreads();
+        g.sync();
     }
-    if (tid == 0) bulk_wait_all();
+    if (g.lane == 0) bulk_wait_all();
 }
 
 // ---- any shape: row stays in global memory (L2), k up to cols -----------------------------------
@@ -223,37 +223,53 @@ int topk_num_columns(uint16_t cols, float ratio) {
     return k;
 }
 
-// Shared-memory bytes the row kernel needs, and the thread count that suits the row length.
-static size_t smem_row_bytes(uint32_t cols) { return (size_t)cols * 4 + sizeof(TopkScratch); }
-static int smem_row_threads(uint32_t cols) { return cols <= 4096 ? 256 : (cols <= 16384 ? 512 : 1024); }
-static cudaError_t prefer_max_smem(const void *kernel, size_t smem) {
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) return err;
-    return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+// Geometry of the group kernel: G warps per row (a group never holds more than 16 KiB of row per warp
+// pair), as many groups per CTA as fit half of an SM's shared memory.
+struct GroupGeometry {
+    int G, groups, threads;
+    unsigned group_bytes, ctl_off;
+};
+static GroupGeometry group_geometry(uint32_t cols) {
+    GroupGeometry f;
+    f.G = cols <= 4096 ? 2 : (cols <= 8192 ? 4 : 8);
+    f.ctl_off = (cols * 4u + 15u) & ~15u;
+    f.group_bytes = (f.ctl_off + (unsigned)sizeof(GroupCtl) + 127u) & ~127u;
+    int groups = (int)((110u * 1024u) / f.group_bytes);
+    if (groups < 1) groups = 1;
+    if (groups > 512 / (32 * f.G)) groups = 512 / (32 * f.G);
+    if (groups > 15) groups = 15;
+    f.groups = groups;
+    f.threads = groups * 32 * f.G;
+    return f;
 }
 
 bool topk_rows_fit_smem(const void *d_in, const void *d_residual, uint32_t cols, uint32_t k) {
-    if (cols % 4 != 0 || k == 0 || k > (uint32_t)kCandCap) return false;
-    if (k > (uint32_t)smem_row_threads(cols)) return false;
-    if (smem_row_bytes(cols) > 200 * 1024 || cols > 4u * (uint32_t)smem_row_threads(cols) * kMaxRowIters) return false;
+    if (cols % 4 != 0 || k == 0 || k > (uint32_t)kCandCap || cols > 24576u) return false;
+    if (group_geometry(cols).group_bytes > 110u * 1024u) return false;
     if (reinterpret_cast<uintptr_t>(d_in) % 16 != 0) return false;
     if (d_residual && reinterpret_cast<uintptr_t>(d_residual) % 16 != 0) return false;
     return true;
 }
 
-template <int NT, int IT>
-static cudaError_t launch_smem(const float *d_in, float *d_residual, uint32_t rows, uint32_t cols, uint32_t k,
-                               uint16_t *d_idx, float *d_val, unsigned *d_status, int sm_count, cudaStream_t stream) {
-    const size_t smem = smem_row_bytes(cols);
-    cudaError_t err = prefer_max_smem(reinterpret_cast<const void *>(topk_rows_smem_kernel<NT, IT>), smem);
+template <int G>
+static cudaError_t launch_group(const float *d_in, float *d_residual, uint32_t rows, uint32_t cols, uint32_t k,
+                                uint16_t *d_idx, float *d_val, unsigned *d_status, int sm_count, cudaStream_t stream) {
+    const GroupGeometry f = group_geometry(cols);
+    const size_t smem = (size_t)f.group_bytes * f.groups;
+    cudaError_t err = cudaFuncSetAttribute(topk_rows_group_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return err;
+    err = cudaFuncSetAttribute(topk_rows_group_kernel<G>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                               cudaSharedmemCarveoutMaxShared);
     if (err != cudaSuccess) return err;
     int per_sm = 0;
-    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, topk_rows_smem_kernel<NT, IT>, NT, smem);
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, topk_rows_group_kernel<G>, f.threads, smem);
     if (err != cudaSuccess) return err;
     if (per_sm < 1) per_sm = 1;
-    unsigned grid = (unsigned)sm_count * (unsigned)per_sm;      // persistent: every CTA resident
-    if (grid > rows) grid = rows;
-    topk_rows_smem_kernel<NT, IT><<<grid, NT, smem, stream>>>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status);
+    unsigned grid = (unsigned)sm_count * (unsigned)per_sm;
+    const unsigned needed = (rows + f.groups - 1) / f.groups;
+    if (grid > needed) grid = needed;
+    topk_rows_group_kernel<G><<<grid, f.threads, smem, stream>>>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status,
+                                                                  f.group_bytes, f.ctl_off);
     return cudaGetLastError();
 }
 
@@ -267,16 +283,11 @@ cudaError_t topk_rows(const float *d_in, float *d_residual, uint32_t rows, uint3
     }
     if (!d_idx || !d_val) return cudaErrorInvalidValue;
     if (topk_rows_fit_smem(d_in, d_residual, cols, k)) {
-        const int nt = smem_row_threads(cols);
-        const bool few = cols <= 16u * (uint32_t)nt;          // at most 4 float4 per thread
-#define BSQ_LAUNCH(NT_) (few ? launch_smem<NT_, 4>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status, sm_count, stream) \
-                             : launch_smem<NT_, 8>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status, sm_count, stream))
-        switch (nt) {
-            case 256: return BSQ_LAUNCH(256);
-            case 512: return BSQ_LAUNCH(512);
-            default: return BSQ_LAUNCH(1024);
+        switch (group_geometry(cols).G) {
+            case 2: return launch_group<2>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status, sm_count, stream);
+            case 4: return launch_group<4>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status, sm_count, stream);
+            default: return launch_group<8>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status, sm_count, stream);
         }
-#undef BSQ_LAUNCH
     }
     unsigned grid = (unsigned)sm_count * 8u;
     if (grid > rows) grid = rows;
