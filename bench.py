@@ -289,10 +289,11 @@ def main():
     del d_out
 
     # ---- max over ranks ----
-    times = torch.tensor([ms_total, e2e_s * 1e3, ms_dec, ms_p1, ms_p2], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms, ms_dec, ms_p1, ms_p2 = [float(v) for v in times.cpu()]
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bsq_shard", os.path.join(entry.PKG_DIR, "shard.py"))
+    shard = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(shard)
+    ms_total, e2e_ms, ms_dec, ms_p1, ms_p2 = shard.max_over_ranks([ms_total, e2e_s * 1e3, ms_dec, ms_p1, ms_p2], device="cuda")
 
     if rank == 0:
         in_bytes = n * 4
