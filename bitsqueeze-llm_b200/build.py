@@ -59,7 +59,7 @@ def build(force=False, verbose=False):
             if code != 0:
                 raise RuntimeError("nvcc failed for " + cmd[-3])
     if jobs or force or not _newer(LIB, objs):
-        cmd = [_nvcc()] + ARCH + ["-shared", "-o", LIB] + objs + ["-lcurand", "-lcusolver"]
+        cmd = [_nvcc()] + ARCH + ["-shared", "-o", LIB] + objs + ["-lcurand", "-lcusolver", "-ldl"]
         code = subprocess.run(cmd, capture_output=True, text=True)
         if code.returncode != 0:
             raise RuntimeError("link failed:\n" + code.stdout + code.stderr)

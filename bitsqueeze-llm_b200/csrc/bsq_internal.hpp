@@ -74,7 +74,11 @@ cudaError_t gemm(bool a_kmajor, bool b_kmajor, const float *A, long lda, const f
                  size_t workspace_bytes, int sm_count, cudaStream_t stream);
 
 struct SvdWorkspace;
+// sums `count` floats at `buf` over all ranks, enqueued on `stream`
+typedef cudaError_t (*SvdAllReduce)(void *ctx, float *buf, size_t count, cudaStream_t stream);
 SvdWorkspace *svd_workspace_create(int m, int n, int k, int niter, int sm_count);
+SvdWorkspace *svd_workspace_create_sharded(int m_local, int n, int k, int niter, int sm_count, SvdAllReduce allreduce,
+                                           void *allreduce_ctx, int m_total);
 void svd_workspace_destroy(SvdWorkspace *ws);
 // A row-major m x n -> U (m x k row-major), S (k, descending), V (n x k row-major).
 cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d_S, float *d_V,

@@ -49,6 +49,9 @@ struct SvdWorkspace {
     curandGenerator_t rng = nullptr;
     cusolverDnHandle_t solver = nullptr;
     gesvdjInfo_t svdj = nullptr;
+    // row-sharded mode: sum a device buffer over all ranks, in stream order (null: single GPU)
+    SvdAllReduce allreduce = nullptr;
+    void *allreduce_ctx = nullptr;
 };
 
 namespace {
@@ -132,7 +135,7 @@ bool alloc_f(float **p, size_t count) {
 // second rows x k buffer; the result ends in Y for 2 passes and in tmp for 1 (returned through *out).
 // r_a / r_b (nullable) receive the triangular factors of the passes (Y_in = Y_out * r_b * r_a).
 cudaError_t orthonormalise(SvdWorkspace *ws, float *Y, float *tmp, int rows, int passes, float *r_a, float *r_b,
-                           float **out, cudaStream_t st) {
+                           float **out, bool sharded_rows, cudaStream_t st) {
     const int k = ws->k;
     float *src = Y, *dst = tmp;
     for (int pass = 0; pass < passes; ++pass) {
@@ -140,6 +143,10 @@ cudaError_t orthonormalise(SvdWorkspace *ws, float *Y, float *tmp, int rows, int
         cudaError_t err = gemm(false, false, src, k, src, k, ws->g, k, k, k, rows, nullptr, nullptr, 0, nullptr, ws->gemm_ws,
                                ws->gemm_ws_bytes, ws->sm_count, st);
         if (err != cudaSuccess) return err;
+        // a row-sharded panel: its Gram matrix is the sum of the shards' (the one exchange per QR pass);
+        // every rank then factors the same k x k matrix and gets bit-identical R
+        if (sharded_rows && ws->allreduce && (err = ws->allreduce(ws->allreduce_ctx, ws->g, (size_t)k * k, st)) != cudaSuccess)
+            return err;
         cholesky_inverse_kernel<<<1, 1024, 0, st>>>(ws->g, k, ws->t, pass == 0 ? r_a : r_b);
         err = cudaGetLastError();
         if (err != cudaSuccess) return err;
@@ -161,19 +168,32 @@ cudaError_t times_w(SvdWorkspace *ws, const float *A, bool w_transposed_product,
     const int rows_out = w_transposed_product ? ws->N : ws->M;
     const int contract = w_transposed_product ? ws->M : ws->N;
     const long ldx = x_colmajor ? contract : ws->k;
-    return gemm(use_a_as_stored, x_colmajor, A, ws->n, X, ldx, C, ws->k, rows_out, ws->k, contract, nullptr, nullptr, 0,
-                nullptr, ws->gemm_ws, ws->gemm_ws_bytes, ws->sm_count, st);
+    cudaError_t err = gemm(use_a_as_stored, x_colmajor, A, ws->n, X, ldx, C, ws->k, rows_out, ws->k, contract, nullptr,
+                           nullptr, 0, nullptr, ws->gemm_ws, ws->gemm_ws_bytes, ws->sm_count, st);
+    // row-sharded W: W^T X contracts over the sharded rows, so the shards' partial products are summed
+    if (err == cudaSuccess && w_transposed_product && ws->allreduce)
+        err = ws->allreduce(ws->allreduce_ctx, C, (size_t)rows_out * ws->k, st);
+    return err;
 }
 
 }  // namespace
 
 SvdWorkspace *svd_workspace_create(int m, int n, int k, int niter, int sm_count) {
+    return svd_workspace_create_sharded(m, n, k, niter, sm_count, nullptr, nullptr, 0);
+}
+
+// Row-sharded: this rank holds m of the m_total rows (all n columns); the working matrix is never the
+// transpose, so that the sharded dimension is the tall one that only GEMMs touch.
+SvdWorkspace *svd_workspace_create_sharded(int m, int n, int k, int niter, int sm_count, SvdAllReduce allreduce,
+                                           void *allreduce_ctx, int m_total) {
     if (m <= 0 || n <= 0 || k <= 0 || niter < 0) return nullptr;
     SvdWorkspace *ws = new (std::nothrow) SvdWorkspace();
     if (!ws) return nullptr;
     ws->m = m; ws->n = n; ws->niter = niter; ws->sm_count = sm_count;
-    ws->k = std::max(1, std::min(k, std::min(m, n)));
-    ws->transposed = m < n;
+    ws->allreduce = allreduce;
+    ws->allreduce_ctx = allreduce_ctx;
+    ws->k = std::max(1, std::min(k, std::min(allreduce ? m_total : m, n)));
+    ws->transposed = allreduce ? false : m < n;
     ws->M = ws->transposed ? n : m;
     ws->N = ws->transposed ? m : n;
     const size_t kk = (size_t)ws->k * ws->k;
@@ -238,21 +258,21 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
     // Y = W Omega, Q = orth(Y).  Panels ping-pong between the two buffers of their size.
     if ((err = times_w(ws, d_A, false, ws->omega, true, ws->y, st)) != cudaSuccess) return err;
     const int last_passes = 2;
-    if ((err = orthonormalise(ws, ws->y, ws->y2, ws->M, ws->niter == 0 ? last_passes : 1, nullptr, nullptr, &q, st)) != cudaSuccess)
+    if ((err = orthonormalise(ws, ws->y, ws->y2, ws->M, ws->niter == 0 ? last_passes : 1, nullptr, nullptr, &q, true, st)) != cudaSuccess)
         return err;
     for (int it = 0; it < ws->niter; ++it) {
         if ((err = times_w(ws, d_A, true, q, false, ws->z, st)) != cudaSuccess) return err;               // Z = W^T Q
-        if ((err = orthonormalise(ws, ws->z, ws->z2, ws->N, 1, nullptr, nullptr, &qz, st)) != cudaSuccess) return err;
+        if ((err = orthonormalise(ws, ws->z, ws->z2, ws->N, 1, nullptr, nullptr, &qz, false, st)) != cudaSuccess) return err;
         spare = (q == ws->y) ? ws->y2 : ws->y;
         if ((err = times_w(ws, d_A, false, qz, false, spare, st)) != cudaSuccess) return err;             // Y = W Qz
         float *other = (spare == ws->y) ? ws->y2 : ws->y;
-        if ((err = orthonormalise(ws, spare, other, ws->M, it + 1 == ws->niter ? last_passes : 1, nullptr, nullptr, &q, st)) !=
+        if ((err = orthonormalise(ws, spare, other, ws->M, it + 1 == ws->niter ? last_passes : 1, nullptr, nullptr, &q, true, st)) !=
             cudaSuccess)
             return err;
     }
     // B^T = W^T Q = Q2 C with C = R2 R1
     if ((err = times_w(ws, d_A, true, q, false, ws->z, st)) != cudaSuccess) return err;
-    if ((err = orthonormalise(ws, ws->z, ws->z2, ws->N, 2, ws->tinv1, ws->tinv2, &qz, st)) != cudaSuccess) return err;
+    if ((err = orthonormalise(ws, ws->z, ws->z2, ws->N, 2, ws->tinv1, ws->tinv2, &qz, false, st)) != cudaSuccess) return err;
     if ((err = gemm(true, false, ws->tinv2, k, ws->tinv1, k, ws->core, k, k, k, k, nullptr, nullptr, 0, nullptr, nullptr, 0,
                     ws->sm_count, st)) != cudaSuccess)
         return err;

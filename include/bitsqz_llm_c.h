@@ -122,6 +122,18 @@ int bsq_svd_lowrank(const float *d_A, int m, int n, int k, int niter, unsigned l
 int bsq_reconstruct(const float *d_U, const float *d_S, const float *d_V, int m, int n, int k, const float *d_minuend,
                     float *d_out, uint32_t *d_flag, void *stream);
 
+/* ---- row-sharded SVD over several GPUs, one process per GPU (no counterpart in the reference, which is
+ * single-GPU; the sharded form of svd_lowrank_cuda, svd_lowrank_cuda.cuh:54-68).  A is split by rows; each
+ * rank passes its m_local x n slice and receives its rows of U; S and V are replicated and bit-identical
+ * on all ranks.  Collectives: NCCL all-reduce of the k x k Gram matrices and the n x k partial products.
+ * Rank 0 makes the 128-byte id and hands it to the others (any side channel), then every rank creates
+ * its communicator with the device it will use current. */
+int bsq_shard_unique_id(void *out, size_t bytes);
+void *bsq_shard_comm_create(const void *unique_id, int rank, int world);
+void bsq_shard_comm_destroy(void *comm);
+int bsq_svd_lowrank_sharded(void *comm, const float *d_A_local, int m_local, int m_total, int n, int k, int niter,
+                            unsigned long long seed, float *d_U_local, float *d_S, float *d_V, void *stream);
+
 /* library build tag: "sm_100a" plus the compile date */
 const char *bsq_build_info(void);
 
