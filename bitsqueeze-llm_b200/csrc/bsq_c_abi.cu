@@ -120,9 +120,15 @@ int bsq_svd_lowrank(const float *d_A, int m, int n, int k, int niter, unsigned l
     SvdWorkspace *ws = svd_workspace_create(m, n, k, niter, device_sm_count());
     if (!ws) return 1;
     const cudaError_t e = svd_lowrank(ws, d_A, d_U, d_S, d_V, seed, nullptr, as_stream(stream));
-    const cudaError_t s = cudaStreamSynchronize(as_stream(stream));     // the workspace dies with this call
+    const cudaError_t s = svd_workspace_finish(ws, as_stream(stream));  // the workspace dies with this call
     svd_workspace_destroy(ws);
     return rc(e) | rc(s);
+}
+int bsq_gemm(int a_kmajor, int b_kmajor, const float *d_A, long lda, const float *d_B, long ldb, float *d_C, long ldc, int M,
+             int N, int K, float *d_workspace, size_t workspace_bytes, int allow_tensor_cores, uint32_t *d_status, void *stream) {
+    if (!d_A || !d_B || !d_C || M <= 0 || N <= 0 || K <= 0) return 1;
+    return rc(gemm_select(allow_tensor_cores != 0, a_kmajor != 0, b_kmajor != 0, d_A, lda, d_B, ldb, d_C, ldc, M, N, K, nullptr,
+                          nullptr, 0, nullptr, d_status, d_workspace, workspace_bytes, device_sm_count(), as_stream(stream)));
 }
 int bsq_reconstruct(const float *d_U, const float *d_S, const float *d_V, int m, int n, int k, const float *d_minuend,
                     float *d_out, uint32_t *d_flag, void *stream) {

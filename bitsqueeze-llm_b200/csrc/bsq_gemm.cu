@@ -19,27 +19,16 @@
 //
 // This version computes on the FP32 pipes (128 x 128 x 16 tiles, 8 x 8 per thread, double-buffered
 // shared memory).
+#include "bsq_gemm.hpp"
 #include "bsq_internal.hpp"
+
+#include <cstdlib>
 
 namespace bsq {
 namespace {
 
 constexpr int BM = 128, BN = 128, BK = 16, GT = 256;
 constexpr int PAD = 4;
-
-struct GemmArgs {
-    const float *A, *B;
-    float *C;                  // output, or partial tiles when splits > 1
-    int M, N, K;
-    long lda, ldb, ldc;
-    const float *kscale;       // nullable: opA(i, kk) *= kscale[kk]
-    int splits;                // K splits (grid.z)
-    int k_per_split;           // multiple of BK
-    long split_stride;         // elements between partial results
-    const float *minuend;      // nullable (only without splits): C = minuend - acc
-    long ldm;
-    unsigned *flag;            // nullable: |= 1 when some |C| > FLT_EPSILON (with minuend)
-};
 
 template <bool KMAJOR>
 __device__ __forceinline__ void load_tile(const float *__restrict__ P, long ld, int rows_total, int k_total, int row0, int k0,
@@ -186,15 +175,67 @@ __global__ void reduce_splits_kernel(const float *__restrict__ part, float *__re
     }
 }
 
+cudaError_t launch_reduce(const float *workspace, float *C, int M, int N, long ldc, int splits, int sm_count,
+                          cudaStream_t stream) {
+    const long total = (long)M * N;
+    long rg = (total + 255) / 256;
+    if (rg > (long)sm_count * 8) rg = (long)sm_count * 8;
+    reduce_splits_kernel<<<(int)rg, 256, 0, stream>>>(workspace, C, M, N, ldc, splits, (long)M * N);
+    return cudaGetLastError();
+}
+
+// BSQ_GEMM_TC=0 keeps every product on the FP32 pipes (for A/B comparisons of the two kernels).
+bool tensor_cores_enabled() {
+    static const bool on = [] {
+        const char *e = std::getenv("BSQ_GEMM_TC");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 }  // namespace
 
 size_t gemm_workspace_bytes(int M, int N, int max_splits) { return (size_t)M * N * max_splits * sizeof(float); }
 
 // Picks the K split so that about two CTAs per SM are busy; partials go to `workspace` (may be null: no split).
 cudaError_t gemm(bool a_kmajor, bool b_kmajor, const float *A, long lda, const float *B, long ldb, float *C, long ldc, int M,
-                 int N, int K, const float *kscale, const float *minuend, long ldm, unsigned *flag, float *workspace,
-                 size_t workspace_bytes, int sm_count, cudaStream_t stream) {
+                 int N, int K, const float *kscale, const float *minuend, long ldm, unsigned *flag, unsigned *status,
+                 float *workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream) {
+    return gemm_select(tensor_cores_enabled(), a_kmajor, b_kmajor, A, lda, B, ldb, C, ldc, M, N, K, kscale, minuend, ldm, flag,
+                       status, workspace, workspace_bytes, sm_count, stream);
+}
+
+cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, const float *A, long lda, const float *B, long ldb,
+                        float *C, long ldc, int M, int N, int K, const float *kscale, const float *minuend, long ldm,
+                        unsigned *flag, unsigned *status, float *workspace, size_t workspace_bytes, int sm_count,
+                        cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
+    if (allow_tensor_cores) {
+        // tensor-core path: one 128-row tile per CTA, one CTA per SM; K is split so that the tiles fill the SMs once
+        GemmArgs t{};
+        t.A = A; t.B = B; t.M = M; t.N = N; t.K = K; t.lda = lda; t.ldb = ldb;
+        t.kscale = kscale; t.minuend = minuend; t.ldm = ldm;
+        const int tiles_tc = (M + 127) / 128;
+        int splits_tc = 1;
+        if (workspace && tiles_tc < sm_count) {
+            const int max_by_k = max(1, K / 64);
+            const int max_by_ws = (int)(workspace_bytes / ((size_t)M * N * sizeof(float)));
+            splits_tc = max(1, min(sm_count / tiles_tc, min(max_by_k, max_by_ws)));
+        }
+        t.splits = splits_tc;
+        t.k_per_split = ((K + splits_tc - 1) / splits_tc + 31) / 32 * 32;
+        t.splits = (K + t.k_per_split - 1) / t.k_per_split;                    // no empty split
+        if (t.splits > 1) {
+            t.C = workspace; t.ldc = N; t.split_stride = (long)M * N;
+        } else {
+            t.C = C; t.ldc = ldc; t.split_stride = 0;
+        }
+        if (gemm_tc_eligible(t, a_kmajor, b_kmajor)) {
+            cudaError_t err = gemm_tc_launch(t, a_kmajor, b_kmajor, status, stream);
+            if (err != cudaSuccess || t.splits == 1) return err;
+            return launch_reduce(workspace, C, M, N, ldc, t.splits, sm_count, stream);
+        }
+    }
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     int splits = 1;
     if (workspace && !minuend && tiles < 2 * sm_count) {
@@ -221,12 +262,7 @@ cudaError_t gemm(bool a_kmajor, bool b_kmajor, const float *A, long lda, const f
     else gemm_kernel<false, false><<<grid, GT, 0, stream>>>(g);
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess || splits == 1) return err;
-    const long total = (long)M * N;
-    long rg = (total + 255) / 256;
-    if (rg > (long)sm_count * 8) rg = (long)sm_count * 8;
-    const int rgrid = (int)rg;
-    reduce_splits_kernel<<<rgrid, 256, 0, stream>>>(workspace, C, M, N, ldc, splits, (long)M * N);
-    return cudaGetLastError();
+    return launch_reduce(workspace, C, M, N, ldc, splits, sm_count, stream);
 }
 
 }  // namespace bsq

@@ -1,0 +1,29 @@
+// Argument block shared by the two GEMM kernels of the low-rank stages (bsq_gemm.cu: FP32 pipes,
+// bsq_gemm_tc.cu: tcgen05 tensor cores with 3xTF32 splitting).
+#pragma once
+
+#include <cuda_runtime.h>
+
+namespace bsq {
+
+// C[M x N] = opA[M x K] * opB[K x N]; see bsq_gemm.cu for the operand conventions.
+struct GemmArgs {
+    const float *A, *B;
+    float *C;                  // output, or partial tiles when splits > 1
+    int M, N, K;
+    long lda, ldb, ldc;
+    const float *kscale;       // nullable: opA(i, kk) *= kscale[kk]
+    int splits;                // K splits (grid.z)
+    int k_per_split;           // multiple of BK
+    long split_stride;         // elements between partial results
+    const float *minuend;      // nullable (only without splits): C = minuend - acc
+    long ldm;
+    unsigned *flag;            // nullable: |= 1 when some |C| > FLT_EPSILON (with minuend)
+};
+
+// Tensor-core path: true if the shape qualifies (N a multiple of 16 up to 256, 16-byte aligned operands with
+// leading dimensions that are multiples of 4, no fused epilogue).  Launches with grid (M tiles, 1, splits).
+bool gemm_tc_eligible(const GemmArgs &g, bool a_kmajor, bool b_kmajor);
+cudaError_t gemm_tc_launch(const GemmArgs &g, bool a_kmajor, bool b_kmajor, unsigned *status, cudaStream_t stream);
+
+}  // namespace bsq

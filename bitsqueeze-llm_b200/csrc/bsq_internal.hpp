@@ -69,9 +69,16 @@ bool topk_rows_fit_smem(const void *d_in, const void *d_residual, uint32_t cols,
 // C[M x N] = opA[M x K] * opB[K x N] in FP32 (bsq_gemm.cu).  a_kmajor: opA(i,kk) = A[i*lda+kk], else A[kk*lda+i];
 // b_kmajor: opB(kk,j) = B[j*ldb+kk], else B[kk*ldb+j].  kscale (nullable) scales opA along K.  minuend (nullable):
 // C = minuend - product, *flag |= 1 when some |C| > FLT_EPSILON.  workspace (nullable) enables a deterministic K split.
+// Skinny products (N = 16..256, no fused epilogue) run on the tensor cores (bsq_gemm_tc.cu); `status` (nullable device
+// word) receives kStatusBarrierTimeout if one of that kernel's bounded waits gives up.
 cudaError_t gemm(bool a_kmajor, bool b_kmajor, const float *A, long lda, const float *B, long ldb, float *C, long ldc, int M,
-                 int N, int K, const float *kscale, const float *minuend, long ldm, unsigned *flag, float *workspace,
-                 size_t workspace_bytes, int sm_count, cudaStream_t stream);
+                 int N, int K, const float *kscale, const float *minuend, long ldm, unsigned *flag, unsigned *status,
+                 float *workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream);
+// The same with the kernel choice explicit: allow_tensor_cores = false keeps the product on the FP32 pipes.
+cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, const float *A, long lda, const float *B, long ldb,
+                        float *C, long ldc, int M, int N, int K, const float *kscale, const float *minuend, long ldm,
+                        unsigned *flag, unsigned *status, float *workspace, size_t workspace_bytes, int sm_count,
+                        cudaStream_t stream);
 
 struct SvdWorkspace;
 // sums `count` floats at `buf` over all ranks, enqueued on `stream`
@@ -83,6 +90,8 @@ void svd_workspace_destroy(SvdWorkspace *ws);
 // A row-major m x n -> U (m x k row-major), S (k, descending), V (n x k row-major).
 cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d_S, float *d_V,
                         unsigned long long seed, unsigned *d_status, cudaStream_t stream);
+// For calls made with d_status == nullptr: waits for the stream and returns an error if a bounded wait gave up.
+cudaError_t svd_workspace_finish(SvdWorkspace *ws, cudaStream_t stream);
 // out = (U diag(S)) V^T, row-major m x n.  d_minuend (nullable): write minuend - out instead and
 // OR 1 into *d_flag when some |difference| > FLT_EPSILON.
 cudaError_t reconstruct_lowrank(const float *d_U, const float *d_S, const float *d_V, int m, int n, int k,

@@ -105,7 +105,7 @@ int bsq_svd_lowrank_sharded(void *comm, const float *d_A_local, int m_local, int
     if (!ws) return 1;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const cudaError_t e = svd_lowrank(ws, d_A_local, d_U_local, d_S, d_V, seed, nullptr, st);
-    const cudaError_t s = cudaStreamSynchronize(st);
+    const cudaError_t s = svd_workspace_finish(ws, st);
     svd_workspace_destroy(ws);
     if (e != cudaSuccess || s != cudaSuccess) {
         cudaGetLastError();

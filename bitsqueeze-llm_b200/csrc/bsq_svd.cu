@@ -52,6 +52,8 @@ struct SvdWorkspace {
     // row-sharded mode: sum a device buffer over all ranks, in stream order (null: single GPU)
     SvdAllReduce allreduce = nullptr;
     void *allreduce_ctx = nullptr;
+    unsigned *status = nullptr;         // device status word of the current call
+    unsigned *own_status = nullptr;     // used when the caller passes none
 };
 
 namespace {
@@ -121,6 +123,99 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_kernel(float *A, int k,
     }
 }
 
+// The same factorisation and inverse for k up to kCholeskySmemMaxK, entirely in shared memory: the upper
+// triangle is held packed (row i at row_off(i) + c, c >= i), k (k + 1) / 2 floats, so k = 256 takes 129 KB.
+// G is only read; R goes to Rcpy, R^-1 to T (both full row-major k x k with zeros below the diagonal).
+// Two CTA barriers per column in the factorisation, two per row in the inversion.
+constexpr int kCholeskySmemMaxK = 320;
+__host__ __device__ constexpr size_t cholesky_smem_bytes(int k) { return ((size_t)k * (k + 1) / 2 + 2 * (size_t)k + 2 * 1024 + 64) * sizeof(float); }
+
+__global__ void __launch_bounds__(1024) cholesky_inverse_smem_kernel(const float *__restrict__ G, int k, float *__restrict__ T,
+                                                                     float *__restrict__ Rcpy) {
+    extern __shared__ float sm[];
+    float *P = sm;                                         // packed upper triangle
+    float *vec = sm + (size_t)k * (k + 1) / 2;             // 2 x k: the scaled pivot row / the row of R being inverted
+    float *part = vec + 2 * k;                             // 2 x 1024: partial sums of the split dot products
+    float *red = part + 2 * 1024;                          // 32 + 1
+    const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
+    auto row_off = [k](int i) { return i * k - (i * (i - 1)) / 2 - i; };
+    float md = 0.0f;
+    for (int e = tid; e < k * k; e += nt) {
+        const int i = e / k, c = e % k;
+        if (c >= i) {
+            const float v = G[e];
+            P[row_off(i) + c] = v;
+            if (c == i) md = fmaxf(md, v);
+        }
+    }
+    for (int d = 16; d > 0; d >>= 1) md = fmaxf(md, __shfl_xor_sync(0xffffffffu, md, d));
+    if (lane == 0) red[warp] = md;
+    __syncthreads();
+    if (tid == 0) {
+        float m = 0.0f;
+        for (int w = 0; w < nwarps; ++w) m = fmaxf(m, red[w]);
+        red[32] = m > 0.0f ? m * 1.0e-5f : 0.0f;
+    }
+    __syncthreads();
+    const float shift = red[32];
+    for (int i = tid; i < k; i += nt) P[row_off(i) + i] += shift;
+    __syncthreads();
+    for (int j = 0; j < k; ++j) {
+        // pivot and scaled row j (every thread derives the pivot itself; it is stored in the next phase)
+        const int oj = row_off(j);
+        float d = P[oj + j];
+        if (!(d > 0.5f * shift)) d = 0.5f * shift;
+        const float r = d > 0.0f ? sqrtf(d) : 0.0f;
+        const float inv = r > 0.0f ? 1.0f / r : 0.0f;
+        for (int c = j + 1 + tid; c < k; c += nt) vec[c] = P[oj + c] * inv;
+        __syncthreads();
+        if (tid == 0) P[oj + j] = r;
+        for (int c = j + 1 + tid; c < k; c += nt) P[oj + c] = vec[c];
+        for (int i = j + 1 + warp; i < k; i += nwarps) {    // trailing update, one warp per row
+            const float rji = vec[i];
+            const int oi = row_off(i);
+            for (int c = i + lane; c < k; c += 32) P[oi + c] -= rji * vec[c];
+        }
+        __syncthreads();
+    }
+    for (int e = tid; e < k * k; e += nt) {                // R out; T's zeros below the diagonal
+        const int i = e / k, c = e % k;
+        if (Rcpy) Rcpy[e] = c < i ? 0.0f : P[row_off(i) + c];
+        if (c < i) T[e] = 0.0f;
+    }
+    __syncthreads();
+    // T = R^-1 in place, row by row from the bottom: T(i,c) = (delta_ic - sum_{l=i+1..c} R(i,l) T(l,c)) / R(i,i).
+    // Column c is served by `ways` threads (one per residue of l); their partial sums are added in a fixed order,
+    // so the result is the same on every run.  vec and part alternate between two copies: the stores of row i - 1
+    // may overtake the last reads of row i.
+    const int ways = max(1, min(32, nt / k));              // 1024 / 256 = 4, 1024 / 128 = 8
+    const int c_of = tid % k, way = tid / k;
+    for (int i = k - 1; i >= 0; --i) {
+        const int oi = row_off(i);
+        float *v = vec + (i & 1) * k, *ps = part + (i & 1) * 1024;
+        for (int c = i + tid; c < k; c += nt) v[c] = P[oi + c];
+        __syncthreads();
+        if (way < ways) {
+            float acc = 0.0f;
+            for (int l = i + 1 + way; l <= c_of; l += ways) acc += v[l] * P[row_off(l) + c_of];
+            ps[way * k + c_of] = acc;
+        }
+        __syncthreads();
+        const float rii = v[i];
+        const float inv = rii > 0.0f ? 1.0f / rii : 0.0f;
+        for (int c = i + tid; c < k; c += nt) {
+            float sum = 0.0f;
+            for (int w = 0; w < ways; ++w) sum += ps[w * k + c];
+            P[oi + c] = ((c == i ? 1.0f : 0.0f) - sum) * inv;
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < k * k; e += nt) {
+        const int i = e / k, c = e % k;
+        if (c >= i) T[e] = P[row_off(i) + c];
+    }
+}
+
 bool alloc_f(float **p, size_t count) {
     if (cudaMalloc(reinterpret_cast<void **>(p), std::max<size_t>(count, 1) * sizeof(float)) != cudaSuccess) {
         cudaGetLastError();
@@ -140,18 +235,22 @@ cudaError_t orthonormalise(SvdWorkspace *ws, float *Y, float *tmp, int rows, int
     float *src = Y, *dst = tmp;
     for (int pass = 0; pass < passes; ++pass) {
         // G = src^T src
-        cudaError_t err = gemm(false, false, src, k, src, k, ws->g, k, k, k, rows, nullptr, nullptr, 0, nullptr, ws->gemm_ws,
+        cudaError_t err = gemm(false, false, src, k, src, k, ws->g, k, k, k, rows, nullptr, nullptr, 0, nullptr, ws->status, ws->gemm_ws,
                                ws->gemm_ws_bytes, ws->sm_count, st);
         if (err != cudaSuccess) return err;
         // a row-sharded panel: its Gram matrix is the sum of the shards' (the one exchange per QR pass);
         // every rank then factors the same k x k matrix and gets bit-identical R
         if (sharded_rows && ws->allreduce && (err = ws->allreduce(ws->allreduce_ctx, ws->g, (size_t)k * k, st)) != cudaSuccess)
             return err;
-        cholesky_inverse_kernel<<<1, 1024, 0, st>>>(ws->g, k, ws->t, pass == 0 ? r_a : r_b);
+        if (k <= kCholeskySmemMaxK) {
+            cholesky_inverse_smem_kernel<<<1, 1024, cholesky_smem_bytes(k), st>>>(ws->g, k, ws->t, pass == 0 ? r_a : r_b);
+        } else {
+            cholesky_inverse_kernel<<<1, 1024, 0, st>>>(ws->g, k, ws->t, pass == 0 ? r_a : r_b);
+        }
         err = cudaGetLastError();
         if (err != cudaSuccess) return err;
         // dst = src T
-        err = gemm(true, false, src, k, ws->t, k, dst, k, rows, k, k, nullptr, nullptr, 0, nullptr, nullptr, 0, ws->sm_count, st);
+        err = gemm(true, false, src, k, ws->t, k, dst, k, rows, k, k, nullptr, nullptr, 0, nullptr, ws->status, nullptr, 0, ws->sm_count, st);
         if (err != cudaSuccess) return err;
         std::swap(src, dst);
     }
@@ -169,7 +268,7 @@ cudaError_t times_w(SvdWorkspace *ws, const float *A, bool w_transposed_product,
     const int contract = w_transposed_product ? ws->M : ws->N;
     const long ldx = x_colmajor ? contract : ws->k;
     cudaError_t err = gemm(use_a_as_stored, x_colmajor, A, ws->n, X, ldx, C, ws->k, rows_out, ws->k, contract, nullptr,
-                           nullptr, 0, nullptr, ws->gemm_ws, ws->gemm_ws_bytes, ws->sm_count, st);
+                           nullptr, 0, nullptr, ws->status, ws->gemm_ws, ws->gemm_ws_bytes, ws->sm_count, st);
     // row-sharded W: W^T X contracts over the sharded rows, so the shards' partial products are summed
     if (err == cudaSuccess && w_transposed_product && ws->allreduce)
         err = ws->allreduce(ws->allreduce_ctx, C, (size_t)rows_out * ws->k, st);
@@ -203,9 +302,10 @@ SvdWorkspace *svd_workspace_create_sharded(int m, int n, int k, int niter, int s
               alloc_f(&ws->t, kk) && alloc_f(&ws->tinv1, kk) && alloc_f(&ws->tinv2, kk) && alloc_f(&ws->core, kk) &&
               alloc_f(&ws->uc, kk) && alloc_f(&ws->vc, kk);
     // split-K partials: up to 2 * SMs tiles' worth of the largest skinny product, and of the Gram matrix
-    ws->gemm_ws_bytes = std::max((size_t)ws->M * ws->k * 4, kk * 2 * (size_t)sm_count) * sizeof(float);
+    ws->gemm_ws_bytes = std::max((size_t)ws->M * ws->k * 8, kk * 2 * (size_t)sm_count) * sizeof(float);
     ok = ok && alloc_f(&ws->gemm_ws, ws->gemm_ws_bytes / sizeof(float));
     ok = ok && cudaMalloc(reinterpret_cast<void **>(&ws->dev_info), sizeof(int)) == cudaSuccess;
+    ok = ok && cudaMalloc(reinterpret_cast<void **>(&ws->own_status), sizeof(unsigned)) == cudaSuccess;
     ok = ok && curandCreateGenerator(&ws->rng, CURAND_RNG_PSEUDO_DEFAULT) == CURAND_STATUS_SUCCESS;
     ok = ok && cusolverDnCreate(&ws->solver) == CUSOLVER_STATUS_SUCCESS;
     ok = ok && cusolverDnCreateGesvdjInfo(&ws->svdj) == CUSOLVER_STATUS_SUCCESS;
@@ -218,6 +318,9 @@ SvdWorkspace *svd_workspace_create_sharded(int m, int n, int k, int niter, int s
         ws->lwork = std::max(1, std::max(l1, l2));
         ok = ok && alloc_f(&ws->solver_work, (size_t)ws->lwork);
     }
+    if (ok && ws->k <= kCholeskySmemMaxK)
+        ok = cudaFuncSetAttribute(cholesky_inverse_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)cholesky_smem_bytes(ws->k)) == cudaSuccess;
     if (!ok) {
         cudaGetLastError();
         svd_workspace_destroy(ws);
@@ -233,6 +336,7 @@ void svd_workspace_destroy(SvdWorkspace *ws) {
     for (float *p : bufs)
         if (p) cudaFree(p);
     if (ws->dev_info) cudaFree(ws->dev_info);
+    if (ws->own_status) cudaFree(ws->own_status);
     if (ws->svdj) cusolverDnDestroyGesvdjInfo(ws->svdj);
     if (ws->solver) cusolverDnDestroy(ws->solver);
     if (ws->rng) curandDestroyGenerator(ws->rng);
@@ -240,11 +344,21 @@ void svd_workspace_destroy(SvdWorkspace *ws) {
     delete ws;
 }
 
+// Waits for the stream and reads the workspace's own status word (calls made without a caller status word).
+cudaError_t svd_workspace_finish(SvdWorkspace *ws, cudaStream_t st) {
+    unsigned h = 0;
+    cudaError_t err = cudaMemcpyAsync(&h, ws->own_status, sizeof(unsigned), cudaMemcpyDeviceToHost, st);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(st);
+    if (err != cudaSuccess) return err;
+    return h == 0 ? cudaSuccess : cudaErrorLaunchTimeout;
+}
+
 cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d_S, float *d_V, unsigned long long seed,
                         unsigned *d_status, cudaStream_t st) {
-    (void)d_status;
     if (!ws || !d_A || !d_U || !d_S || !d_V) return cudaErrorInvalidValue;
     const int k = ws->k;
+    ws->status = d_status ? d_status : ws->own_status;    // bounded waits of the tensor-core GEMMs report here
+    if (!d_status && cudaMemsetAsync(ws->own_status, 0, sizeof(unsigned), st) != cudaSuccess) return cudaErrorUnknown;
     if (curandSetStream(ws->rng, st) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
     if (cusolverDnSetStream(ws->solver, st) != CUSOLVER_STATUS_SUCCESS) return cudaErrorUnknown;
     if (curandSetPseudoRandomGeneratorSeed(ws->rng, seed) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
@@ -273,7 +387,7 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
     // B^T = W^T Q = Q2 C with C = R2 R1
     if ((err = times_w(ws, d_A, true, q, false, ws->z, st)) != cudaSuccess) return err;
     if ((err = orthonormalise(ws, ws->z, ws->z2, ws->N, 2, ws->tinv1, ws->tinv2, &qz, false, st)) != cudaSuccess) return err;
-    if ((err = gemm(true, false, ws->tinv2, k, ws->tinv1, k, ws->core, k, k, k, k, nullptr, nullptr, 0, nullptr, nullptr, 0,
+    if ((err = gemm(true, false, ws->tinv2, k, ws->tinv1, k, ws->core, k, k, k, k, nullptr, nullptr, 0, nullptr, ws->status, nullptr, 0,
                     ws->sm_count, st)) != cudaSuccess)
         return err;
     // The row-major C read as column-major is C^T = Vc S Uc^T: the solver's "U" is Vc, its "V" is Uc.
@@ -283,10 +397,10 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
     // W = (Q Vc) S (Q2 Uc)^T; both k x k factors are column-major, i.e. K-major B operands
     float *d_left = ws->transposed ? d_V : d_U;            // M x k factor
     float *d_right = ws->transposed ? d_U : d_V;           // N x k factor
-    if ((err = gemm(true, true, q, k, ws->vc, k, d_left, k, ws->M, k, k, nullptr, nullptr, 0, nullptr, nullptr, 0,
+    if ((err = gemm(true, true, q, k, ws->vc, k, d_left, k, ws->M, k, k, nullptr, nullptr, 0, nullptr, ws->status, nullptr, 0,
                     ws->sm_count, st)) != cudaSuccess)
         return err;
-    return gemm(true, true, qz, k, ws->uc, k, d_right, k, ws->N, k, k, nullptr, nullptr, 0, nullptr, nullptr, 0,
+    return gemm(true, true, qz, k, ws->uc, k, d_right, k, ws->N, k, k, nullptr, nullptr, 0, nullptr, ws->status, nullptr, 0,
                 ws->sm_count, st);
 }
 
@@ -294,7 +408,7 @@ cudaError_t reconstruct_lowrank(const float *d_U, const float *d_S, const float 
                                 const float *d_minuend, float *d_out, unsigned *d_flag, int sm_count, cudaStream_t st) {
     if (!d_U || !d_S || !d_V || !d_out || m <= 0 || n <= 0 || k <= 0) return cudaErrorInvalidValue;
     // out(i, j) = sum_t (U(i, t) S(t)) V(j, t): A = U as stored with a per-k scale, B = V^T (K-major)
-    return gemm(true, true, d_U, k, d_V, k, d_out, n, m, n, k, d_S, d_minuend, n, d_flag, nullptr, 0, sm_count, st);
+    return gemm(true, true, d_U, k, d_V, k, d_out, n, m, n, k, d_S, d_minuend, n, d_flag, nullptr, nullptr, 0, sm_count, st);
 }
 
 }  // namespace bsq

@@ -122,6 +122,16 @@ int bsq_svd_lowrank(const float *d_A, int m, int n, int k, int niter, unsigned l
 int bsq_reconstruct(const float *d_U, const float *d_S, const float *d_V, int m, int n, int k, const float *d_minuend,
                     float *d_out, uint32_t *d_flag, void *stream);
 
+/* The FP32 matrix product inside the two stages above, where the reference calls cublasSgemm
+ * (svd_lowrank_cuda.cu:293-309, reconstruct_lowrank_cuda.cu:46-61): C[M x N] = opA[M x K] * opB[K x N], all row-major
+ * device arrays.  a_kmajor: opA(i,kk) = A[i*lda+kk], else A[kk*lda+i]; b_kmajor: opB(kk,j) = B[j*ldb+kk], else B[kk*ldb+j].
+ * d_workspace (nullable) allows a deterministic split of K.  allow_tensor_cores = 0 keeps the product on the FP32 pipes;
+ * otherwise products with N a multiple of 16 up to 256 run as 3xTF32 on the tensor cores (FP32-level accuracy).
+ * d_status (nullable) receives bit 0 if a bounded wait inside the tensor-core kernel gave up.  Exported so that the
+ * kernel can be tested and timed on its own. */
+int bsq_gemm(int a_kmajor, int b_kmajor, const float *d_A, long lda, const float *d_B, long ldb, float *d_C, long ldc, int M,
+             int N, int K, float *d_workspace, size_t workspace_bytes, int allow_tensor_cores, uint32_t *d_status, void *stream);
+
 /* ---- row-sharded SVD over several GPUs, one process per GPU (no counterpart in the reference, which is
  * single-GPU; the sharded form of svd_lowrank_cuda, svd_lowrank_cuda.cuh:54-68).  A is split by rows; each
  * rank passes its m_local x n slice and receives its rows of U; S and V are replicated and bit-identical
