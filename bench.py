@@ -319,7 +319,7 @@ def main():
             "decompress": {"value": dec_value, "unit": "GB/s (FP32 output)", "ms_per_step": ms_dec / args.steps,
                            "stages": "nf4dq dequantise + outlier scatter-add, device resident"},
             "gpu_launches": 2 * args.steps,
-            "roofline": {"bound": "hbm", "kernel": "frontend_pass1_kernel<2,true> (2 warps per row)", "achieved": ach_p1, "peak": peak,
+            "roofline": {"bound": "hbm", "kernel": "frontend_select_kernel<4> (4 warps per row)", "achieved": ach_p1, "peak": peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": ach_p1 / peak, "traffic": None,
                          "ms_per_launch": ms_p1, "pass2_ms_per_launch": ms_p2,
                          "stage": {"achieved": ach_stage, "frac": ach_stage / peak, "bytes": bytes_stage}},
