@@ -211,16 +211,18 @@ cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, c
                         cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
     if (allow_tensor_cores) {
-        // tensor-core path: one 128-row tile per CTA, one CTA per SM; K is split so that the tiles fill the SMs once
+        // tensor-core path: one 128-row tile per CTA, two CTAs per SM up to N = 128; K is split so that the tiles fill
+        // the SMs once
         GemmArgs t{};
         t.A = A; t.B = B; t.M = M; t.N = N; t.K = K; t.lda = lda; t.ldb = ldb;
         t.kscale = kscale; t.minuend = minuend; t.ldm = ldm;
         const int tiles_tc = (M + 127) / 128;
         int splits_tc = 1;
-        if (workspace && tiles_tc < sm_count) {
+        const int slots = (N <= 128 ? 2 : 1) * sm_count;
+        if (workspace && tiles_tc < slots) {
             const int max_by_k = max(1, K / 64);
             const int max_by_ws = (int)(workspace_bytes / ((size_t)M * N * sizeof(float)));
-            splits_tc = max(1, min(sm_count / tiles_tc, min(max_by_k, max_by_ws)));
+            splits_tc = max(1, min(slots / tiles_tc, min(max_by_k, max_by_ws)));
         }
         t.splits = splits_tc;
         t.k_per_split = ((K + splits_tc - 1) / splits_tc + 31) / 32 * 32;

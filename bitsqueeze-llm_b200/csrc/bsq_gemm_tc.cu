@@ -15,10 +15,12 @@
 //     and lo*hi + hi*lo into a second one, added in the epilogue (the dropped lo*lo term and the
 //     rounding of lo are ~2^-22 relative; the tensor core truncates when it accumulates, which leaves
 //     an error of a few 1e-7 of sum |a||b| for K in the thousands, against a few 1e-8 on the FP32 pipes);
-//   * two shared-memory stages: the loads and splits of chunk c+1 overlap the MMAs of chunk c;
-//     tcgen05.commit on an mbarrier tells when a stage may be overwritten and when the tile is done;
-//   * the 128 x N FP32 tile is read back with tcgen05.ld (one accumulator row per thread) and written
-//     to C or to the K-split workspace.
+//   * 256 threads stage 16 of K at a time and keep the global loads of three such chunks in flight in
+//     registers, so HBM latency hides behind the staging of earlier chunks; two shared-memory stages:
+//     the splits of chunk c+1 overlap the MMAs of chunk c; tcgen05.commit on an mbarrier tells when a
+//     stage may be overwritten and when the tile is done; two CTAs share an SM when N <= 128;
+//   * the 128 x N FP32 tile is read back with tcgen05.ld (two threads per accumulator row, half the
+//     columns each) and written to C or to the K-split workspace.
 // Every mbarrier wait is bounded; on a timeout the CTA records it in the status word, still frees its
 // tensor memory and leaves.
 #include "bsq_device.cuh"
@@ -28,8 +30,9 @@ namespace bsq {
 namespace {
 
 constexpr int TM = 128;          // output rows per CTA (UMMA M)
-constexpr int TK = 32;           // K per shared-memory stage (four k-steps of 8)
-constexpr int NT = 128;          // threads: one accumulator row each in the epilogue
+constexpr int TK = 16;           // K per shared-memory stage (two k-steps of 8)
+constexpr int NT = 256;          // threads: all stage operands, one issues the MMAs, two per accumulator row in the epilogue
+constexpr int DEPTH = 3;         // chunks of K in flight in registers per thread
 
 __device__ __forceinline__ uint64_t smem_desc(unsigned addr_bytes, unsigned lbo_bytes, unsigned sbo_bytes) {
     // start address, leading / stride byte offsets in 16-byte units; version 1 (bits 46-47); no swizzle
@@ -75,85 +78,99 @@ __device__ __forceinline__ void split_store(float4 v, float4 *hi, float4 *lo) {
 // Shared-memory position (in 16-byte units) of the 4 consecutive k values kc*4 .. kc*4+3 of row/column r (the MN
 // index) of an operand chunk: the tensor core's canonical K-major layout without swizzle.  A core matrix is 8
 // consecutive r at one kc (8 x 16 B); core matrices follow one another along MN every 144 B (SBO, padded from 128 B)
-// and along K every lbo_units(extent) * 16 B (LBO, padded to an odd number of units): with these paddings both
-// staging patterns below store without bank conflicts.
-__host__ __device__ constexpr unsigned lbo_units(int extent) { return (unsigned)(extent / 8) * 9u + 1u; }
+// and along K every lbo_units(extent) * 16 B (LBO, padded to 2 modulo 8 units): with these paddings both staging
+// patterns below store without bank conflicts.
+__host__ __device__ constexpr unsigned lbo_units(int extent) {
+    return (unsigned)(extent / 8) * 9u + (10u - ((unsigned)(extent / 8) * 9u) % 8u) % 8u;
+}
 __host__ __device__ constexpr unsigned stage_units(int extent) { return (TK / 4) * lbo_units(extent); }
 __device__ __forceinline__ unsigned unit_index(int kc, int r, int extent) {
     return (unsigned)kc * lbo_units(extent) + (unsigned)(r >> 3) * 9u + (unsigned)(r & 7);
 }
 
-// One operand chunk: `extent` (MN) x TK (K) starting at (mn0, k0), read from a row-major array in which either K
-// (KMAJOR) or MN is the contiguous dimension; consecutive threads read consecutive 16-byte pieces of global
-// memory.  A K-contiguous float4 is one unit of the layout; MN-contiguous sources are transposed in registers,
-// four float4 of consecutive k giving four units.
-template <bool KMAJOR, int MAXU>
-struct Stager {
-    float4 regs[MAXU];
-    __device__ __forceinline__ void load(const float *__restrict__ P, long ld, int mn_total, int k_end, int mn0, int k0,
-                                         int extent) {
-        const int units = extent * (TK / 4);
+// A thread's share of one operand chunk (extent x TK): four float4, fixed over the K loop.  Threads 0-127 serve A
+// (one slot each, TM = 128 slots), threads 128-255 serve B (N slots, one or two each).
+//   K-major source (K contiguous in global memory): slot s holds k quad kc = s % 4 of the four rows
+//       s / 4 + j * extent / 4, j = 0..3, so four neighbouring threads read 64 contiguous bytes of a row;
+//   MN-major source: slot s holds 4 consecutive MN indices x 4 consecutive k (four 16-byte loads from four k rows,
+//       neighbouring threads neighbouring 16-byte pieces), transposed in registers so that each output unit again
+//       holds 4 consecutive k of one MN index.
+// Either way a slot fills four 16-byte units of the K-major layout above, hi and lo.  Everything address-like is
+// worked out once; per chunk a slot costs four loads, the splits and eight stores.
+struct Item {
+    float4 v[4];
+};
+
+template <bool KMAJOR>
+struct Slot {
+    const float *src;        // chunk 0
+    long step;               // elements from one chunk to the next
+    long off[4];             // elements from src to each of the four loads
+    unsigned unit[4];        // 16-byte unit of each output in the operand stage
+    int kq;                  // k quad of the slot (K-major: of all four loads; MN-major: the loads are its four k)
+    bool active;
+
+    // Rows / columns past the end of the matrix (last tile of A) are read from valid memory instead (the last row,
+    // or the row's leading elements): what they produce lands in accumulator rows that are never written out.
+    __device__ __forceinline__ void init(const float *P, long ld, int mn_total, int mn0, int k_begin, int extent, int s) {
+        active = s < extent;
+        const int ss = active ? s : 0;
         if (KMAJOR) {
+            kq = ss % 4;
+            const int r0 = ss / 4, rstep = extent / 4;
+            src = P + k_begin + kq * 4;
 #pragma unroll
-            for (int i = 0; i < MAXU; ++i) {
-                const int f = threadIdx.x + i * NT;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                const int kc = f % (TK / 4), r = f / (TK / 4);
-                const int gk = k0 + kc * 4, gr = mn0 + r;
-                if (f < units && gr < mn_total && gk < k_end) {
-                    const float *src = P + (long)gr * ld + gk;
-                    if (gk + 3 < k_end) v = *reinterpret_cast<const float4 *>(src);
-                    else { v.x = src[0]; if (gk + 1 < k_end) v.y = src[1]; if (gk + 2 < k_end) v.z = src[2]; }
-                }
-                regs[i] = v;
+            for (int j = 0; j < 4; ++j) {
+                unit[j] = unit_index(kq, r0 + j * rstep, extent);
+                off[j] = (long)min(mn0 + r0 + j * rstep, mn_total - 1) * ld;
             }
+            step = TK;
         } else {
             const int e4 = extent / 4;
+            const int mn4 = ss % e4;
+            kq = ss / e4;
+            const int gmn = mn0 + mn4 * 4;
+            src = P + (long)(k_begin + kq * 4) * ld + (gmn < mn_total ? gmn : 0);
 #pragma unroll
-            for (int i = 0; i < MAXU / 4; ++i) {
-                const int f = threadIdx.x + i * NT;          // item: 4 MN values x 4 k values
-                const int mn4 = f % e4, kq = f / e4;
-                const int gmn = mn0 + mn4 * 4;
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    const int gk = k0 + kq * 4 + t;
-                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (f * 4 < units && gk < k_end && gmn < mn_total) {
-                        const float *src = P + (long)gk * ld + gmn;
-                        if (gmn + 3 < mn_total) v = *reinterpret_cast<const float4 *>(src);
-                        else { v.x = src[0]; if (gmn + 1 < mn_total) v.y = src[1]; if (gmn + 2 < mn_total) v.z = src[2]; }
-                    }
-                    regs[i * 4 + t] = v;
-                }
+            for (int j = 0; j < 4; ++j) {
+                unit[j] = unit_index(kq, mn4 * 4 + j, extent);
+                off[j] = (long)j * ld;
             }
+            step = (long)TK * ld;
         }
     }
-    __device__ __forceinline__ void store(float4 *hi, float4 *lo, int extent) const {
-        const int units = extent * (TK / 4);
+    // whole chunk
+    __device__ __forceinline__ void load(Item &it, int c) const {
+        const float *p = src + (long)c * step;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) it.v[j] = *reinterpret_cast<const float4 *>(p + off[j]);
+    }
+    // last chunk of a K range that is no multiple of TK: only k_left of its TK values exist
+    __device__ __forceinline__ void load_checked(Item &it, int c, int k_left) const {
+        const float *p = src + (long)c * step;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (KMAJOR) {
+                const int left = k_left - kq * 4;
+                if (left >= 4) v = *reinterpret_cast<const float4 *>(p + off[j]);
+                else if (left > 0) { v.x = p[off[j]]; if (left > 1) v.y = p[off[j] + 1]; if (left > 2) v.z = p[off[j] + 2]; }
+            } else if (kq * 4 + j < k_left) {
+                v = *reinterpret_cast<const float4 *>(p + off[j]);
+            }
+            it.v[j] = v;
+        }
+    }
+    __device__ __forceinline__ void store(const Item &it, float4 *hi, float4 *lo) const {
         if (KMAJOR) {
 #pragma unroll
-            for (int i = 0; i < MAXU; ++i) {
-                const int f = threadIdx.x + i * NT;
-                if (f < units) {
-                    const unsigned u = unit_index(f % (TK / 4), f / (TK / 4), extent);
-                    split_store(regs[i], hi + u, lo + u);
-                }
-            }
+            for (int j = 0; j < 4; ++j) split_store(it.v[j], hi + unit[j], lo + unit[j]);
         } else {
-            const int e4 = extent / 4;
-#pragma unroll
-            for (int i = 0; i < MAXU / 4; ++i) {
-                const int f = threadIdx.x + i * NT;
-                if (f * 4 < units) {
-                    const int mn4 = f % e4, kq = f / e4;
-                    const float4 v0 = regs[i * 4], v1 = regs[i * 4 + 1], v2 = regs[i * 4 + 2], v3 = regs[i * 4 + 3];
-                    const unsigned u = unit_index(kq, mn4 * 4, extent);          // mn4 * 4 .. + 3 stay inside one core matrix
-                    split_store(make_float4(v0.x, v1.x, v2.x, v3.x), hi + u, lo + u);
-                    split_store(make_float4(v0.y, v1.y, v2.y, v3.y), hi + u + 1, lo + u + 1);
-                    split_store(make_float4(v0.z, v1.z, v2.z, v3.z), hi + u + 2, lo + u + 2);
-                    split_store(make_float4(v0.w, v1.w, v2.w, v3.w), hi + u + 3, lo + u + 3);
-                }
-            }
+            const float4 v0 = it.v[0], v1 = it.v[1], v2 = it.v[2], v3 = it.v[3];
+            split_store(make_float4(v0.x, v1.x, v2.x, v3.x), hi + unit[0], lo + unit[0]);
+            split_store(make_float4(v0.y, v1.y, v2.y, v3.y), hi + unit[1], lo + unit[1]);
+            split_store(make_float4(v0.z, v1.z, v2.z, v3.z), hi + unit[2], lo + unit[2]);
+            split_store(make_float4(v0.w, v1.w, v2.w, v3.w), hi + unit[3], lo + unit[3]);
         }
     }
 };
@@ -169,14 +186,14 @@ __global__ void __launch_bounds__(NT) gemm_tc_kernel(GemmArgs g, unsigned *statu
     __shared__ __align__(8) uint64_t bar_free[2];
     __shared__ __align__(8) uint64_t bar_done;
     __shared__ unsigned tmem_base_slot;
+    constexpr int ITEMS = NMAX / (NT - TM);                   // slots of B per serving thread: 1 (N <= 128) or 2
     const int tid = threadIdx.x, warp = tid >> 5;
     const int N = g.N;                                        // multiple of 16, <= NMAX
     const int m0 = blockIdx.x * TM;
     const int k_begin = blockIdx.z * g.k_per_split;
     const int k_end = min(g.K, k_begin + g.k_per_split);
     const unsigned a_units = stage_units(TM), b_units = stage_units(N);
-    // stage s: [A hi | A lo | B hi | B lo]
-    const unsigned stage_bytes = (2 * a_units + 2 * b_units) * 16u;
+    const unsigned stage_bytes = (2 * a_units + 2 * b_units) * 16u;       // stage: [A hi | A lo | B hi | B lo]
     // two accumulators: the hi*hi chain and, half the allocation further on, the two small cross terms
     const unsigned acc_cols = N <= 16 ? 16u : (N <= 32 ? 32u : (N <= 64 ? 64u : (N <= 128 ? 128u : 256u)));
     const unsigned tmem_cols = 2u * acc_cols;
@@ -198,64 +215,100 @@ __global__ void __launch_bounds__(NT) gemm_tc_kernel(GemmArgs g, unsigned *statu
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_d = tmem_base_slot;
 
-    // instruction descriptor: FP32 accumulate, TF32 x TF32, majors, N >> 3, M >> 4
-    // (both operands are K-major in shared memory whatever their orientation in global memory)
+    // instruction descriptor: FP32 accumulate, TF32 x TF32, both operands K-major in shared memory, N >> 3, M >> 4
     const unsigned idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned)(N >> 3) << 17) | ((unsigned)(TM >> 4) << 24);
 
-    Stager<A_KMAJOR, TM * (TK / 4) / NT> sa;
-    Stager<B_KMAJOR, NMAX * (TK / 4) / NT> sb;
+    // threads 0-127: one slot of A each; threads 128-255: one or two slots of B each
+    const bool serves_a = tid < TM;
+    Slot<A_KMAJOR> slot_a;
+    Slot<B_KMAJOR> slot_b[ITEMS];
+    slot_a.init(g.A, g.lda, g.M, m0, k_begin, TM, serves_a ? tid : TM);
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) slot_b[i].init(g.B, g.ldb, N, 0, k_begin, N, serves_a ? N : tid - TM + i * (NT - TM));
+    Item regs[DEPTH][ITEMS];
+    auto load_chunk = [&](Item(&r)[ITEMS], int c, int k_left) {
+        if (k_left >= TK) {
+            if (serves_a) {
+                slot_a.load(r[0], c);
+            } else {
+#pragma unroll
+                for (int i = 0; i < ITEMS; ++i)
+                    if (slot_b[i].active) slot_b[i].load(r[i], c);
+            }
+        } else if (serves_a) {
+            slot_a.load_checked(r[0], c, k_left);
+        } else {
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i)
+                if (slot_b[i].active) slot_b[i].load_checked(r[i], c, k_left);
+        }
+    };
+    auto store_chunk = [&](const Item(&r)[ITEMS], float4 *a_hi, float4 *a_lo, float4 *b_hi, float4 *b_lo) {
+        if (serves_a) {
+            slot_a.store(r[0], a_hi, a_lo);
+        } else {
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i)
+                if (slot_b[i].active) slot_b[i].store(r[i], b_hi, b_lo);
+        }
+    };
+
     const int chunks = (k_end - k_begin + TK - 1) / TK;
     bool ok = true;
     unsigned free_phase = 0;                                  // bit s: parity of the next wait on bar_free[s]
-    if (chunks > 0) {
-        sa.load(g.A, g.lda, g.M, k_end, m0, k_begin, TM);
-        sb.load(g.B, g.ldb, N, k_end, 0, k_begin, N);
-    }
-    for (int c = 0; c < chunks && ok; ++c) {
-        const int s = c & 1;
-        bool mine = true;
-        if (c >= 2) {                                         // the MMAs of chunk c-2 must be done with stage s
-            mine = mbar_wait_bounded(&bar_free[s], (free_phase >> s) & 1u, status);
-            free_phase ^= 1u << s;
-        }
-        float4 *a_hi = reinterpret_cast<float4 *>(smem_raw + (size_t)s * stage_bytes), *a_lo = a_hi + a_units, *b_hi = a_lo + a_units, *b_lo = b_hi + b_units;
-        sa.store(a_hi, a_lo, TM);
-        sb.store(b_hi, b_lo, N);
-        fence_proxy_async_smem();                             // generic-proxy stores -> tensor-core (async proxy) reads
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        ok = __syncthreads_and(mine) != 0;                    // uniform: after a timeout nobody issues or loops on
-        if (tid == 0 && ok) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const unsigned a_hi_addr = smem_u32(a_hi), a_lo_addr = smem_u32(a_lo);
-            const unsigned b_hi_addr = smem_u32(b_hi), b_lo_addr = smem_u32(b_lo);
 #pragma unroll
-            for (int ks = 0; ks < TK / 8; ++ks) {
-                const uint64_t dah = kstep_desc(a_hi_addr, ks, TM), dal = kstep_desc(a_lo_addr, ks, TM);
-                const uint64_t dbh = kstep_desc(b_hi_addr, ks, N), dbl = kstep_desc(b_lo_addr, ks, N);
-                mma_tf32(tmem_d, dah, dbh, idesc, c > 0 || ks > 0);
-                mma_tf32(tmem_d + acc_cols, dal, dbh, idesc, c > 0 || ks > 0);
-                mma_tf32(tmem_d + acc_cols, dah, dbl, idesc, true);
+    for (int d = 0; d < DEPTH; ++d)
+        if (d < chunks) load_chunk(regs[d], d, k_end - k_begin - d * TK);
+    for (int c0 = 0; c0 < chunks && ok; c0 += DEPTH) {
+#pragma unroll
+        for (int d = 0; d < DEPTH; ++d) {
+            const int c = c0 + d;
+            if (c < chunks && ok) {                           // uniform over the CTA
+                const int s = c & 1;
+                bool mine = true;
+                if (c >= 2) {                                 // the MMAs of chunk c-2 must be done with stage s
+                    mine = mbar_wait_bounded(&bar_free[s], (free_phase >> s) & 1u, status);
+                    free_phase ^= 1u << s;
+                }
+                float4 *a_hi = reinterpret_cast<float4 *>(smem_raw + (size_t)s * stage_bytes), *a_lo = a_hi + a_units,
+                       *b_hi = a_lo + a_units, *b_lo = b_hi + b_units;
+                store_chunk(regs[d], a_hi, a_lo, b_hi, b_lo);
+                if (c + DEPTH < chunks) load_chunk(regs[d], c + DEPTH, k_end - k_begin - (c + DEPTH) * TK);
+                fence_proxy_async_smem();                     // generic-proxy stores -> tensor-core (async proxy) reads
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                ok = __syncthreads_and(mine) != 0;            // uniform: after a timeout nobody issues or loops on
+                if (tid == 0 && ok) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const unsigned a_hi_addr = smem_u32(a_hi), a_lo_addr = smem_u32(a_lo);
+                    const unsigned b_hi_addr = smem_u32(b_hi), b_lo_addr = smem_u32(b_lo);
+#pragma unroll
+                    for (int ks = 0; ks < TK / 8; ++ks) {
+                        const uint64_t dah = kstep_desc(a_hi_addr, ks, TM), dal = kstep_desc(a_lo_addr, ks, TM);
+                        const uint64_t dbh = kstep_desc(b_hi_addr, ks, N), dbl = kstep_desc(b_lo_addr, ks, N);
+                        mma_tf32(tmem_d, dah, dbh, idesc, c > 0 || ks > 0);
+                        mma_tf32(tmem_d + acc_cols, dal, dbh, idesc, c > 0 || ks > 0);
+                        mma_tf32(tmem_d + acc_cols, dah, dbl, idesc, true);
+                    }
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                     smem_u32(c + 1 == chunks ? &bar_done : &bar_free[s]))
+                                 : "memory");
+                }
             }
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                             smem_u32(c + 1 == chunks ? &bar_done : &bar_free[s]))
-                         : "memory");
-        }
-        if (c + 1 < chunks) {                                 // next chunk's loads overlap the MMAs
-            sa.load(g.A, g.lda, g.M, k_end, m0, k_begin + (c + 1) * TK, TM);
-            sb.load(g.B, g.ldb, N, k_end, 0, k_begin + (c + 1) * TK, N);
         }
     }
-    // epilogue: thread t of warp w owns accumulator row 32 w + t
+    // epilogue: accumulator row 32 (w % 4) + lane; warps 0-3 take the lower half of the columns, warps 4-7 the upper
     if (chunks > 0 && ok) ok = mbar_wait_bounded(&bar_done, 0, status);
     ok = __syncthreads_and(ok) != 0;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     float *C = g.C + (long)blockIdx.z * g.split_stride;
-    const int row = m0 + tid;
+    const int row = m0 + (warp & 3) * 32 + (tid & 31);
+    const int half = (N / 16 + 1) / 2 * 16;                  // columns of the lower half, a multiple of 16
+    const int c_begin = warp < 4 ? 0 : half, c_end = warp < 4 ? half : N;
     if (ok) {
-        for (int c0 = 0; c0 < N; c0 += 16) {
+        for (int c0 = c_begin; c0 < c_end; c0 += 16) {
             unsigned r[16], q[16];
             if (chunks > 0) {
-                const unsigned taddr = tmem_d + ((unsigned)(warp * 32) << 16) + (unsigned)c0;
+                const unsigned taddr = tmem_d + ((unsigned)((warp & 3) * 32) << 16) + (unsigned)c0;
                 tmem_ld16(taddr, r);
                 tmem_ld16(taddr + acc_cols, q);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -281,16 +334,17 @@ __global__ void __launch_bounds__(NT) gemm_tc_kernel(GemmArgs g, unsigned *statu
     }
 }
 
-template <int NMAX>
-size_t tc_smem_bytes(bool a_kmajor, bool b_kmajor, int N) {
-    (void)a_kmajor;
-    (void)b_kmajor;
-    return (size_t)2 * (2 * stage_units(TM) + 2 * stage_units(N)) * 16;
+// Two stages of [A hi | A lo | B hi | B lo]; padded so that no more CTAs share an SM than their tensor-memory
+// allocations (2 * N columns of 512) allow: a CTA too many would sit in tcgen05.alloc until another one leaves.
+size_t tc_smem_bytes(int N) {
+    const size_t need = (size_t)2 * (2 * stage_units(TM) + 2 * stage_units(N)) * 16;
+    const size_t floor = N > 128 ? 116 * 1024 : (N > 64 ? 78 * 1024 : (N > 32 ? 56 * 1024 : 0));
+    return need > floor ? need : floor;
 }
 
 template <bool AK, bool BK, int NMAX>
 cudaError_t launch(const GemmArgs &g, unsigned *status, cudaStream_t stream) {
-    const size_t smem = tc_smem_bytes<NMAX>(AK, BK, g.N);
+    const size_t smem = tc_smem_bytes(g.N);
     cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<AK, BK, NMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return err;
     dim3 grid((g.M + TM - 1) / TM, 1, g.splits);
