@@ -33,6 +33,7 @@ constexpr int TM = 128;          // output rows per CTA (UMMA M)
 constexpr int TK = 16;           // K per shared-memory stage (two k-steps of 8)
 constexpr int NT = 256;          // threads: all stage operands, one issues the MMAs, two per accumulator row in the epilogue
 constexpr int DEPTH = 3;         // chunks of K in flight in registers per thread
+constexpr int STAGES = 2;        // operand stages in shared memory (three measured slower: less L1 left for the loads)
 
 __device__ __forceinline__ uint64_t smem_desc(unsigned addr_bytes, unsigned lbo_bytes, unsigned sbo_bytes) {
     // start address, leading / stride byte offsets in 16-byte units; version 1 (bits 46-47); no swizzle
@@ -61,10 +62,11 @@ __device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned (&r)[16]) {
         : "r"(taddr));
 }
 
+// Round to TF32 (10 mantissa bits), ties away from zero, by integer arithmetic on the bit pattern: two full-rate
+// instructions (add half of the last kept place, clear the 13 low bits; a carry out of the mantissa bumps the exponent
+// as it should).  Same result as cvt.rna.tf32.f32 for every finite value.
 __device__ __forceinline__ float tf32_rna(float x) {
-    unsigned r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
+    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
 }
 
 // x = hi + lo + e with hi, lo exactly representable in TF32 and |e| <= 2^-22 |x|
@@ -183,7 +185,7 @@ __device__ __forceinline__ uint64_t kstep_desc(unsigned stage_addr, int ks, int 
 template <bool A_KMAJOR, bool B_KMAJOR, int NMAX>
 __global__ void __launch_bounds__(NT) gemm_tc_kernel(GemmArgs g, unsigned *status) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bar_free[2];
+    __shared__ __align__(8) uint64_t bar_free[STAGES];
     __shared__ __align__(8) uint64_t bar_done;
     __shared__ unsigned tmem_base_slot;
     constexpr int ITEMS = NMAX / (NT - TM);                   // slots of B per serving thread: 1 (N <= 128) or 2
@@ -199,8 +201,8 @@ __global__ void __launch_bounds__(NT) gemm_tc_kernel(GemmArgs g, unsigned *statu
     const unsigned tmem_cols = 2u * acc_cols;
 
     if (tid == 0) {
-        mbar_init(&bar_free[0], 1);
-        mbar_init(&bar_free[1], 1);
+#pragma unroll
+        for (int i = 0; i < STAGES; ++i) mbar_init(&bar_free[i], 1);
         mbar_init(&bar_done, 1);
         mbar_fence_init();
     }
@@ -264,9 +266,9 @@ __global__ void __launch_bounds__(NT) gemm_tc_kernel(GemmArgs g, unsigned *statu
         for (int d = 0; d < DEPTH; ++d) {
             const int c = c0 + d;
             if (c < chunks && ok) {                           // uniform over the CTA
-                const int s = c & 1;
+                const int s = c % STAGES;
                 bool mine = true;
-                if (c >= 2) {                                 // the MMAs of chunk c-2 must be done with stage s
+                if (c >= STAGES) {                            // the MMAs of chunk c - STAGES must be done with stage s
                     mine = mbar_wait_bounded(&bar_free[s], (free_phase >> s) & 1u, status);
                     free_phase ^= 1u << s;
                 }
@@ -334,10 +336,10 @@ __global__ void __launch_bounds__(NT) gemm_tc_kernel(GemmArgs g, unsigned *statu
     }
 }
 
-// Two stages of [A hi | A lo | B hi | B lo]; padded so that no more CTAs share an SM than their tensor-memory
+// STAGES stages of [A hi | A lo | B hi | B lo]; padded so that no more CTAs share an SM than their tensor-memory
 // allocations (2 * N columns of 512) allow: a CTA too many would sit in tcgen05.alloc until another one leaves.
 size_t tc_smem_bytes(int N) {
-    const size_t need = (size_t)2 * (2 * stage_units(TM) + 2 * stage_units(N)) * 16;
+    const size_t need = (size_t)STAGES * (2 * stage_units(TM) + 2 * stage_units(N)) * 16;
     const size_t floor = N > 128 ? 116 * 1024 : (N > 64 ? 78 * 1024 : (N > 32 ? 56 * 1024 : 0));
     return need > floor ? need : floor;
 }

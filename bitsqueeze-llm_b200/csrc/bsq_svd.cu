@@ -54,6 +54,8 @@ struct SvdWorkspace {
     void *allreduce_ctx = nullptr;
     unsigned *status = nullptr;         // device status word of the current call
     unsigned *own_status = nullptr;     // used when the caller passes none
+    bool seeded = false;                // the generator holds `seed` (seeding costs a kernel of its own)
+    unsigned long long seed = 0;
 };
 
 namespace {
@@ -216,6 +218,179 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_smem_kernel(const float
     }
 }
 
+// The same again for k <= kCholeskyBlockedMaxK, by 32 x 32 blocks, which takes the number of CTA-wide barriers from
+// four per column to a handful per block column.  The block-upper-triangular matrix lives in shared memory
+// (block (I, J), I <= J, at blk_id(I, J)); k is padded to a multiple of 32 with an identity.
+//   factorisation, per block column J: warp 0 factors the diagonal block in registers (one column per lane, the
+//       pivot row travels by shuffles); every thread then solves one column of the block row against it
+//       (R_JJ^T Y = G_JC, forward substitution), and all threads apply the rank-32 update to the trailing blocks;
+//       every sum runs in the order of the unblocked algorithm, so R comes out bit-identical to it;
+//   inverse: the diagonal blocks are inverted by one warp each, all at once; block column J of T = R^-1 is then
+//       T_IJ = -(sum_{L=I..J-1} T_IL R_LJ) T_JJ, two rounds of 32 x 32 block products per column.
+constexpr int kCholeskyBlockedMaxK = 256;
+constexpr int kCB = 32;
+__host__ __device__ constexpr int chol_blocks(int k) { return (k + kCB - 1) / kCB; }
+__host__ __device__ constexpr size_t cholesky_blocked_smem_bytes(int k) {
+    // packed blocks + inverted diagonal blocks + one temporary block column + 1 / diagonal + scalars
+    return ((size_t)(chol_blocks(k) * (chol_blocks(k) + 1) / 2 + 2 * chol_blocks(k)) * kCB * kCB + (size_t)chol_blocks(k) * kCB + 64) *
+           sizeof(float);
+}
+__device__ __forceinline__ int blk_id(int I, int J, int nb) { return I * nb - (I * (I - 1)) / 2 + (J - I); }
+
+__global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const float *__restrict__ G, int k, float *__restrict__ T,
+                                                                        float *__restrict__ Rcpy) {
+    extern __shared__ float sm[];
+    const int nb = chol_blocks(k), nbt = nb * (nb + 1) / 2;
+    float *blocks = sm;                                    // nbt blocks of 32 x 32, row-major
+    float *tinv = blocks + (size_t)nbt * kCB * kCB;        // nb inverted diagonal blocks
+    float *tmp = tinv + (size_t)nb * kCB * kCB;            // nb blocks: one block column of partial products
+    float *dinv = tmp + (size_t)nb * kCB * kCB;            // 1 / R(i, i)
+    float *red = dinv + nb * kCB;                          // 32 + 1
+    const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
+    // load, padded with an identity; the part of a diagonal block below the diagonal is never read
+    float md = 0.0f;
+    for (int e = tid; e < nbt * kCB * kCB; e += nt) {
+        const int b = e / (kCB * kCB), w = e % (kCB * kCB);
+        int I = 0, rem = b;
+        while (rem >= nb - I) { rem -= nb - I; ++I; }      // block (I, I + rem)
+        const int i = I * kCB + w / kCB, c = (I + rem) * kCB + w % kCB;
+        float v = (i == c) ? 1.0f : 0.0f;
+        if (i < k && c < k) v = G[(size_t)i * k + c];
+        blocks[e] = v;
+        if (i == c && i < k) md = fmaxf(md, v);
+    }
+    for (int d = 16; d > 0; d >>= 1) md = fmaxf(md, __shfl_xor_sync(0xffffffffu, md, d));
+    if (lane == 0) red[warp] = md;
+    __syncthreads();
+    if (tid == 0) {
+        float m = 0.0f;
+        for (int w = 0; w < nwarps; ++w) m = fmaxf(m, red[w]);
+        red[32] = m > 0.0f ? m * 1.0e-5f : 0.0f;
+    }
+    __syncthreads();
+    const float shift = red[32];
+    for (int i = tid; i < k; i += nt) blocks[(size_t)blk_id(i / kCB, i / kCB, nb) * kCB * kCB + (i % kCB) * (kCB + 1)] += shift;
+    __syncthreads();
+
+    for (int J = 0; J < nb; ++J) {
+        float *D = blocks + (size_t)blk_id(J, J, nb) * kCB * kCB;
+        if (warp == 0) {                                    // diagonal block: lane c keeps column c
+            float a[kCB];
+#pragma unroll
+            for (int i = 0; i < kCB; ++i) a[i] = D[i * kCB + lane];
+            float my_inv = 0.0f;
+#pragma unroll
+            for (int j = 0; j < kCB; ++j) {
+                float d = __shfl_sync(0xffffffffu, a[j], j);
+                if (!(d > 0.5f * shift)) d = 0.5f * shift;
+                const float r = d > 0.0f ? sqrtf(d) : 0.0f;
+                const float inv = r > 0.0f ? 1.0f / r : 0.0f;
+                a[j] = (lane == j) ? r : a[j] * inv;
+                if (lane == j) my_inv = inv;
+#pragma unroll
+                for (int i = j + 1; i < kCB; ++i) {
+                    const float rji = __shfl_sync(0xffffffffu, a[j], i);
+                    a[i] -= rji * a[j];
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kCB; ++i) D[i * kCB + lane] = (i <= lane) ? a[i] : 0.0f;
+            dinv[J * kCB + lane] = my_inv;
+        }
+        __syncthreads();
+        // block row J: one thread per column, forward substitution with R_JJ^T
+        for (int col = tid; col < (nb - J - 1) * kCB; col += nt) {
+            float *X = blocks + (size_t)blk_id(J, J + 1 + col / kCB, nb) * kCB * kCB + col % kCB;
+            float y[kCB];
+#pragma unroll
+            for (int i = 0; i < kCB; ++i) {
+                float acc = X[i * kCB];
+#pragma unroll
+                for (int l = 0; l < i; ++l) acc -= D[l * kCB + i] * y[l];
+                y[i] = acc * dinv[J * kCB + i];
+            }
+#pragma unroll
+            for (int i = 0; i < kCB; ++i) X[i * kCB] = y[i];
+        }
+        __syncthreads();
+        // trailing blocks (A, B), J < A <= B: G_AB -= R_JA^T R_JB, one 32 x 32 block per pass
+        {
+            const int rest = nb - J - 1, pairs = rest * (rest + 1) / 2;
+            const int i = tid / kCB, c = tid % kCB;
+            for (int pr = 0; pr < pairs; ++pr) {
+                int A = 0, rem = pr;
+                while (rem >= rest - A) { rem -= rest - A; ++A; }
+                const int B = A + rem;
+                const float *RA = blocks + (size_t)blk_id(J, J + 1 + A, nb) * kCB * kCB;
+                const float *RB = blocks + (size_t)blk_id(J, J + 1 + B, nb) * kCB * kCB;
+                float *O = blocks + (size_t)blk_id(J + 1 + A, J + 1 + B, nb) * kCB * kCB;
+                float acc = O[i * kCB + c];
+#pragma unroll
+                for (int l = 0; l < kCB; ++l) acc -= RA[l * kCB + i] * RB[l * kCB + c];
+                O[i * kCB + c] = acc;
+            }
+        }
+        __syncthreads();
+    }
+    // R out; zeros of T below the diagonal; the diagonal blocks' inverses, one warp each
+    for (int e = tid; e < k * k; e += nt) {
+        const int i = e / k, c = e % k;
+        if (Rcpy) Rcpy[e] = c < i ? 0.0f : blocks[(size_t)blk_id(i / kCB, c / kCB, nb) * kCB * kCB + (i % kCB) * kCB + c % kCB];
+        if (c < i) T[e] = 0.0f;
+    }
+    if (warp < nb) {
+        const float *D = blocks + (size_t)blk_id(warp, warp, nb) * kCB * kCB;
+        float a[kCB], t[kCB];
+#pragma unroll
+        for (int i = 0; i < kCB; ++i) { a[i] = D[i * kCB + lane]; t[i] = 0.0f; }
+        const float my_inv = dinv[warp * kCB + lane];
+#pragma unroll
+        for (int i = kCB - 1; i >= 0; --i) {
+            float acc = (lane == i) ? 1.0f : 0.0f;
+#pragma unroll
+            for (int l = i + 1; l < kCB; ++l) acc -= __shfl_sync(0xffffffffu, a[i], l) * t[l];
+            const float inv = __shfl_sync(0xffffffffu, my_inv, i);
+            t[i] = (lane >= i) ? acc * inv : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < kCB; ++i) tinv[(size_t)warp * kCB * kCB + i * kCB + lane] = t[i];
+    }
+    __syncthreads();
+    // block column J of T, from the left: needs T_IL for L < J (already in place) and R_LJ (still in place)
+    {
+        const int i = tid / kCB, c = tid % kCB;
+        for (int J = 1; J < nb; ++J) {
+            for (int I = 0; I < J; ++I) {
+                float acc = 0.0f;
+                for (int L = I; L < J; ++L) {
+                    const float *TL = (L == I) ? tinv + (size_t)I * kCB * kCB : blocks + (size_t)blk_id(I, L, nb) * kCB * kCB;
+                    const float *RL = blocks + (size_t)blk_id(L, J, nb) * kCB * kCB;
+#pragma unroll
+                    for (int l = 0; l < kCB; ++l) acc += TL[i * kCB + l] * RL[l * kCB + c];
+                }
+                tmp[(size_t)I * kCB * kCB + i * kCB + c] = acc;
+            }
+            __syncthreads();
+            const float *TJ = tinv + (size_t)J * kCB * kCB;
+            for (int I = 0; I < J; ++I) {
+                float acc = 0.0f;
+#pragma unroll
+                for (int l = 0; l < kCB; ++l) acc -= tmp[(size_t)I * kCB * kCB + i * kCB + l] * TJ[l * kCB + c];
+                blocks[(size_t)blk_id(I, J, nb) * kCB * kCB + i * kCB + c] = acc;
+            }
+            __syncthreads();
+        }
+    }
+    for (int e = tid; e < k * k; e += nt) {
+        const int i = e / k, c = e % k;
+        if (c >= i) {
+            const int I = i / kCB, Jb = c / kCB;
+            const float *src = (I == Jb) ? tinv + (size_t)I * kCB * kCB : blocks + (size_t)blk_id(I, Jb, nb) * kCB * kCB;
+            T[e] = src[(i % kCB) * kCB + c % kCB];
+        }
+    }
+}
+
 bool alloc_f(float **p, size_t count) {
     if (cudaMalloc(reinterpret_cast<void **>(p), std::max<size_t>(count, 1) * sizeof(float)) != cudaSuccess) {
         cudaGetLastError();
@@ -242,7 +417,10 @@ cudaError_t orthonormalise(SvdWorkspace *ws, float *Y, float *tmp, int rows, int
         // every rank then factors the same k x k matrix and gets bit-identical R
         if (sharded_rows && ws->allreduce && (err = ws->allreduce(ws->allreduce_ctx, ws->g, (size_t)k * k, st)) != cudaSuccess)
             return err;
-        if (k <= kCholeskySmemMaxK) {
+        if (k <= kCholeskyBlockedMaxK) {
+            cholesky_inverse_blocked_kernel<<<1, 1024, cholesky_blocked_smem_bytes(k), st>>>(ws->g, k, ws->t,
+                                                                                                pass == 0 ? r_a : r_b);
+        } else if (k <= kCholeskySmemMaxK) {
             cholesky_inverse_smem_kernel<<<1, 1024, cholesky_smem_bytes(k), st>>>(ws->g, k, ws->t, pass == 0 ? r_a : r_b);
         } else {
             cholesky_inverse_kernel<<<1, 1024, 0, st>>>(ws->g, k, ws->t, pass == 0 ? r_a : r_b);
@@ -318,7 +496,10 @@ SvdWorkspace *svd_workspace_create_sharded(int m, int n, int k, int niter, int s
         ws->lwork = std::max(1, std::max(l1, l2));
         ok = ok && alloc_f(&ws->solver_work, (size_t)ws->lwork);
     }
-    if (ok && ws->k <= kCholeskySmemMaxK)
+    if (ok && ws->k <= kCholeskyBlockedMaxK)
+        ok = cudaFuncSetAttribute(cholesky_inverse_blocked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)cholesky_blocked_smem_bytes(ws->k)) == cudaSuccess;
+    else if (ok && ws->k <= kCholeskySmemMaxK)
         ok = cudaFuncSetAttribute(cholesky_inverse_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)cholesky_smem_bytes(ws->k)) == cudaSuccess;
     if (!ok) {
@@ -361,7 +542,12 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
     if (!d_status && cudaMemsetAsync(ws->own_status, 0, sizeof(unsigned), st) != cudaSuccess) return cudaErrorUnknown;
     if (curandSetStream(ws->rng, st) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
     if (cusolverDnSetStream(ws->solver, st) != CUSOLVER_STATUS_SUCCESS) return cudaErrorUnknown;
-    if (curandSetPseudoRandomGeneratorSeed(ws->rng, seed) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
+    if (!ws->seeded || ws->seed != seed) {
+        if (curandSetPseudoRandomGeneratorSeed(ws->rng, seed) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
+        ws->seeded = true;
+        ws->seed = seed;
+    }
+    // back to the start of the seed's sequence: every call draws the same Omega
     if (curandSetGeneratorOffset(ws->rng, 0ULL) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
     size_t count = (size_t)ws->N * k;
     count += count & 1;                                   // the normal generator wants an even count
