@@ -14,8 +14,8 @@ NF4_DQ quantiser) over one matrix.
   e2e    the same metric through the public bitsqz_llm_compress call with a pinned HOST matrix:
          host->device copy of the input and device->host copy of the packed object inside the
          timed region.
-  roofline      dominant kernel (pass 1: bulk row load, top-k selection, block maxima) from per-pass
-                CUDA events; algorithmic bytes per launch / duration against the measured HBM peak.
+  roofline      dominant kernel (frontend_select_kernel: row sweep, top-k selection, block maxima) from
+                per-kernel CUDA events; algorithmic bytes per launch / duration against the measured HBM peak.
   cpu_baseline  rank 0, N=1: the same workload on the host cores -- reference CPU NF4_DQ quantiser
                 (oracle/_ref, built from the reference's own sources) behind the oracle's top-k port
                 (the reference has no CPU top-k).
@@ -41,6 +41,9 @@ import __graft_entry__ as entry  # noqa: E402
 
 ROWS, COLS, OUTLIER_RATIO, METHOD = 4096, 4096, 0.01, 10
 NBUF = 4
+# dram__bytes_read.sum + dram__bytes_write.sum of one frontend_select_kernel launch on this workload, from the ncu
+# capture summarised in profiles/frontend_nf4dq_c2_4096x4096.md (67 174 400 + 502 272)
+NCU_TRAFFIC_SELECT = 67676672
 METRIC = "FP32-input GB/s, compress (outlier top-k 0.01 + NF4_DQ) of a 4096x4096 FP32 matrix"
 
 
@@ -157,6 +160,93 @@ def run_reference(args, rank):
     print(json.dumps(line))
 
 
+# BASELINE.json configs[2] and configs[3]: 8192 x 4096, seeded synthetic.
+SVD_CONFIGS = {
+    # name: outlier ratio, error ratio, rank, niters, U/V format, S format
+    "C3": dict(outlier=0.0, error=0.0, rank=128, niters=2, uv=-1, s=-1),
+    "C4": dict(outlier=0.005, error=0.01, rank=256, niters=2, uv=11, s=-1),
+}
+
+
+def make_svd_matrix(name, torch):
+    m, n, r = 8192, 4096, 512
+    g = torch.Generator(device="cuda").manual_seed(3)
+    g1, _ = torch.linalg.qr(torch.randn(m, r, device="cuda", generator=g, dtype=torch.float64))
+    g2, _ = torch.linalg.qr(torch.randn(n, r, device="cuda", generator=g, dtype=torch.float64))
+    sv = torch.arange(1, r + 1, device="cuda", dtype=torch.float64) ** -1.0
+    a = (g1 * sv) @ g2.T + 0.01 * torch.randn(m, n, device="cuda", generator=g, dtype=torch.float64)
+    if name == "C4":                                   # outlier channels and heavy-tailed entries on top
+        cols = torch.randperm(n, device="cuda", generator=g)[: max(1, round(0.0005 * n))]
+        a[:, cols] *= 50.0
+        mask = torch.rand(m, n, device="cuda", generator=g) < 0.01
+        z = torch.randn(m, n, device="cuda", generator=g, dtype=torch.float64)
+        chi = (torch.randn(3, m, n, device="cuda", generator=g, dtype=torch.float64) ** 2).sum(0) / 3.0
+        a = torch.where(mask, a + 0.01 * z / chi.sqrt(), a)
+    return a.float().contiguous()
+
+
+def run_svd_config(args):
+    """Side measurement (not the bench line): bitsqz_llm_compress / decompress of an SVD configuration with a device
+    input.  --impl ours times this library; --impl reference times the reference's own CUDA build from oracle/_ref
+    (these stages have no CPU path in the reference)."""
+    import torch
+    cfg = SVD_CONFIGS[args.svd]
+    a = make_svd_matrix(args.svd, torch)
+    m, n = a.shape
+    steps, warm = max(3, min(args.steps, 20)), max(2, min(args.warmup, 5))
+
+    def rel_frob(x, y):
+        return float((x.double() - y.double()).norm() / x.double().norm())
+
+    def timed(fn):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(steps):
+            t0 = time.perf_counter()
+            fn()
+            torch.cuda.synchronize()
+            ts.append((time.perf_counter() - t0) * 1e3)
+        return statistics.median(ts)
+
+    out = {"svd_config": args.svd, "impl": args.impl, "shape": [m, n], "steps": steps}
+    y = torch.zeros_like(a)
+    if args.impl == "ours":
+        pkg = entry.load_package()
+        L = pkg.lib()
+        assert L.bsq_compress_initialize(m, n, cfg["outlier"], cfg["error"], cfg["rank"], cfg["niters"], cfg["uv"], cfg["s"], -1, 1) == 0
+        assert L.bsq_decompress_initialize(m, n, cfg["outlier"], cfg["error"], cfg["rank"], cfg["uv"], cfg["s"], -1) == 0
+        blob = pkg.compress_to_bytes(a.data_ptr())[1]
+        out["compress_ms"] = timed(lambda: pkg.compress_to_bytes(a.data_ptr()))
+        out["decompress_ms"] = timed(lambda: pkg.decompress_packed(blob, y.data_ptr(), m * n))
+        L.bsq_compress_release()
+        L.bsq_decompress_release()
+    else:
+        try:
+            ref = entry.load_oracle().RefCuda()
+        except (FileNotFoundError, OSError) as e:
+            print(json.dumps({"svd_config": args.svd, "impl": "reference", "unavailable": "oracle/_ref/libref_cuda.so not built: %s" % e}))
+            return
+        assert ref.lib.ref_compress_initialize(m, n, cfg["outlier"], cfg["error"], cfg["rank"], cfg["niters"], cfg["uv"], cfg["s"], -1, 1) == 0
+        assert ref.lib.ref_decompress_initialize(m, n, cfg["outlier"], cfg["error"], cfg["rank"], cfg["uv"], cfg["s"], -1) == 0
+        blob = ref.compress_bytes(a.data_ptr())
+
+        def rdec():
+            h = ref.lib.ref_load_from_buffer(blob.ctypes.data, blob.size)
+            rc = ref.lib.ref_decompress(h, y.data_ptr(), m * n)
+            ref.lib.ref_free(h)
+            assert rc == 0
+        out["compress_ms"] = timed(lambda: ref.compress_bytes(a.data_ptr()))
+        out["decompress_ms"] = timed(rdec)
+        ref.lib.ref_compress_release()
+        ref.lib.ref_decompress_release()
+    out["rel_frob"] = rel_frob(a, y)
+    out["bytes"] = int(blob.size)
+    out["fp32_input_gbs_compress"] = m * n * 4 / (out["compress_ms"] * 1e-3) / 1e9
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -165,7 +255,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--stage-only", action="store_true",
                     help="run only the device-stage loop (for profiler captures); prints no bench line")
+    ap.add_argument("--svd", default=None, choices=["C3", "C4"],
+                    help="side measurement, not the bench line: time bitsqz_llm_compress / decompress of an SVD "
+                         "configuration (device input); with --impl reference the reference's own CUDA build is timed")
     args = ap.parse_args()
+    if args.svd:
+        run_svd_config(args)
+        return
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -320,7 +416,7 @@ def main():
                            "stages": "nf4dq dequantise + outlier scatter-add, device resident"},
             "gpu_launches": 2 * args.steps,
             "roofline": {"bound": "hbm", "kernel": "frontend_select_kernel<4> (4 warps per row)", "achieved": ach_p1, "peak": peak,
-                         "peak_kind": peak_kind, "unit": "GB/s", "frac": ach_p1 / peak, "traffic": None,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": ach_p1 / peak, "traffic": NCU_TRAFFIC_SELECT,
                          "ms_per_launch": ms_p1, "pass2_ms_per_launch": ms_p2,
                          "stage": {"achieved": ach_stage, "frac": ach_stage / peak, "bytes": bytes_stage}},
             "clocks": clocks,

@@ -55,7 +55,7 @@ __device__ __forceinline__ unsigned stream_next_row(const RowGroup<G> &g, GroupC
 
 // NF4_DQ kernel 1: selection + block maxima + global maximum.
 template <int G>
-__global__ void __launch_bounds__(256, 3)
+__global__ void __launch_bounds__(256, 4)
     frontend_select_kernel(const float *__restrict__ in, unsigned rows, unsigned cols, unsigned k,
                            uint16_t *__restrict__ out_idx, float *__restrict__ out_val, float *__restrict__ absmax_scratch,
                            unsigned *gmax_bits, unsigned *row_counter) {
@@ -98,7 +98,7 @@ __device__ __forceinline__ void encode_and_store(const RowGroup<G> &g, GroupCtl 
 
 // NF4_DQ kernel 2: rows newest-first.
 template <int G>
-__global__ void __launch_bounds__(256, 3)
+__global__ void __launch_bounds__(256, 4)
     frontend_encode_kernel(const float *__restrict__ in, unsigned rows, unsigned cols, unsigned k,
                            const uint16_t *__restrict__ idx, const float *__restrict__ absmax_scratch,
                            const unsigned *__restrict__ gmax_bits, float *__restrict__ dq_out,
