@@ -26,6 +26,7 @@
 #include <cusolverDn.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <new>
 
 namespace bsq {
@@ -54,6 +55,7 @@ struct SvdWorkspace {
     void *allreduce_ctx = nullptr;
     unsigned *status = nullptr;         // device status word of the current call
     unsigned *own_status = nullptr;     // used when the caller passes none
+    bool own_core_svd = false;          // k small enough for jacobi_svd_kernel (else cuSOLVER's gesvdj on the core)
     bool seeded = false;                // the generator holds `seed` (seeding costs a kernel of its own)
     unsigned long long seed = 0;
 };
@@ -391,6 +393,136 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const fl
     }
 }
 
+// SVD of the k x k core for k <= kJacobiMaxK: one-sided (Hestenes) Jacobi in one CTA, everything in shared memory.
+// The reference runs cusolverDnSgesvd on the k x n matrix B (svd_lowrank_cuda.cu:399-440); here only the k x k
+// triangular factor is left to decompose.
+//   in : C, row-major k x k; read as the column-major matrix M = C^T (column j = row j of C)
+//   out: M = U diag(S) V^T with S descending; U and V column-major k x k
+// Column pairs (p, q) are rotated until all columns of M V are orthogonal to tol (LAPACK's sgesvj criterion,
+// |m_p . m_q| <= tol |m_p| |m_q|, tol = sqrt(len) eps); the k / 2 pairs of a round are disjoint (round-robin
+// schedule), 16 lanes serve a pair, a CTA barrier separates the rounds.  Squared column norms are carried along
+// through the rotations and recomputed exactly at the start of every sweep.  At the end S(j) = |column j|,
+// U(:, j) = column j / S(j) (zero for S(j) = 0), and a rank by counting puts S in descending order.
+constexpr int kJacobiMaxK = 128;
+constexpr int kJacobiMaxSweeps = 30;
+__host__ __device__ constexpr int jacobi_len(int k) { return k <= 64 ? 64 : 128; }
+__host__ __device__ constexpr size_t jacobi_smem_bytes(int k) {
+    return ((size_t)2 * ((k + 1) & ~1) * jacobi_len(k) + 2 * (size_t)((k + 1) & ~1) + 64) * sizeof(float);
+}
+
+__global__ void __launch_bounds__(1024) jacobi_svd_kernel(const float *__restrict__ C, int k, float *__restrict__ S,
+                                                          float *__restrict__ Ucol, float *__restrict__ Vcol) {
+    extern __shared__ __align__(16) float sm[];
+    const int LEN = jacobi_len(k), kp = (k + 1) & ~1, npairs = kp / 2;
+    float *M = sm, *V = M + (size_t)kp * LEN, *nrm = V + (size_t)kp * LEN;
+    int *rank_of = reinterpret_cast<int *>(nrm + kp);
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const int slot = tid >> 4, l = tid & 15;                  // 16 lanes per pair, 64 pair slots
+    const int F4 = LEN / 64;                                  // float4 per lane and column
+    for (int e = tid; e < kp * LEN; e += nt) {
+        const int j = e / LEN, i = e % LEN;
+        M[e] = (j < k && i < k) ? C[(size_t)j * k + i] : 0.0f;
+        V[e] = (i == j && j < k) ? 1.0f : 0.0f;
+    }
+    __syncthreads();
+    const float tol = sqrtf((float)LEN) * 5.9604645e-08f;
+    auto dot16 = [&](float x) {                               // sum over the 16 lanes of a pair slot
+        x += __shfl_xor_sync(0xffffffffu, x, 8, 16);
+        x += __shfl_xor_sync(0xffffffffu, x, 4, 16);
+        x += __shfl_xor_sync(0xffffffffu, x, 2, 16);
+        x += __shfl_xor_sync(0xffffffffu, x, 1, 16);
+        return x;
+    };
+    for (int sweep = 0; sweep < kJacobiMaxSweeps; ++sweep) {
+        for (int j = slot; j < kp; j += nt / 16) {            // exact squared norms
+            float acc = 0.0f;
+            for (int f = 0; f < F4; ++f) {
+                const float4 a = reinterpret_cast<const float4 *>(M + (size_t)j * LEN)[f * 16 + l];
+                acc += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+            }
+            acc = dot16(acc);
+            if (l == 0) nrm[j] = acc;
+        }
+        __syncthreads();
+        bool rotated = false;
+        for (int r = 0; r < kp - 1; ++r) {
+            const bool active = slot < npairs;
+            int p = 0, q = 0;
+            if (active) {
+                if (slot == 0) { p = kp - 1; q = r; }
+                else { p = (r + slot) % (kp - 1); q = (r + kp - 1 - slot) % (kp - 1); }
+            }
+            float4 *mp = reinterpret_cast<float4 *>(M + (size_t)p * LEN), *mq = reinterpret_cast<float4 *>(M + (size_t)q * LEN);
+            float4 ap[2], aq[2];
+            float g = 0.0f;
+#pragma unroll
+            for (int f = 0; f < 2; ++f) {
+                if (f < F4) {
+                    ap[f] = mp[f * 16 + l];
+                    aq[f] = mq[f * 16 + l];
+                    g += ap[f].x * aq[f].x + ap[f].y * aq[f].y + ap[f].z * aq[f].z + ap[f].w * aq[f].w;
+                }
+            }
+            g = dot16(g);
+            const float alpha = nrm[p], beta = nrm[q];
+            if (active && alpha > 0.0f && beta > 0.0f && fabsf(g) > tol * sqrtf(alpha) * sqrtf(beta)) {
+                const float zeta = (beta - alpha) / (2.0f * g);
+                // 1 / (2 zeta) once zeta^2 would overflow: the rotation is then too small to change anything
+                const float t = fabsf(zeta) > 1.0e8f ? 0.5f / zeta : copysignf(1.0f, zeta) / (fabsf(zeta) + sqrtf(1.0f + zeta * zeta));
+                const float c = rsqrtf(1.0f + t * t), sn = c * t;
+                float4 *vp = reinterpret_cast<float4 *>(V + (size_t)p * LEN), *vq = reinterpret_cast<float4 *>(V + (size_t)q * LEN);
+#pragma unroll
+                for (int f = 0; f < 2; ++f) {
+                    if (f < F4) {
+                        const float4 x = ap[f], y = aq[f];
+                        mp[f * 16 + l] = make_float4(c * x.x - sn * y.x, c * x.y - sn * y.y, c * x.z - sn * y.z, c * x.w - sn * y.w);
+                        mq[f * 16 + l] = make_float4(sn * x.x + c * y.x, sn * x.y + c * y.y, sn * x.z + c * y.z, sn * x.w + c * y.w);
+                        const float4 u = vp[f * 16 + l], w = vq[f * 16 + l];
+                        vp[f * 16 + l] = make_float4(c * u.x - sn * w.x, c * u.y - sn * w.y, c * u.z - sn * w.z, c * u.w - sn * w.w);
+                        vq[f * 16 + l] = make_float4(sn * u.x + c * w.x, sn * u.y + c * w.y, sn * u.z + c * w.z, sn * u.w + c * w.w);
+                    }
+                }
+                if (l == 0) {
+                    nrm[p] = fmaxf(alpha - t * g, 0.0f);
+                    nrm[q] = beta + t * g;
+                }
+                rotated = rotated || sn != 0.0f;
+            }
+            __syncthreads();
+        }
+        if (!__syncthreads_or(rotated)) break;
+    }
+    // singular values, order, output
+    for (int j = slot; j < kp; j += nt / 16) {
+        float acc = 0.0f;
+        for (int f = 0; f < F4; ++f) {
+            const float4 a = reinterpret_cast<const float4 *>(M + (size_t)j * LEN)[f * 16 + l];
+            acc += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        }
+        acc = dot16(acc);
+        if (l == 0) nrm[j] = sqrtf(acc);
+    }
+    __syncthreads();
+    for (int j = tid; j < k; j += nt) {
+        const float sj = nrm[j];
+        int rk = 0;
+        for (int i = 0; i < k; ++i) {
+            const float si = nrm[i];
+            rk += (si > sj || (si == sj && i < j)) ? 1 : 0;
+        }
+        rank_of[j] = rk;
+        S[rk] = sj;
+    }
+    __syncthreads();
+    for (int e = tid; e < k * k; e += nt) {
+        const int j = e / k, i = e % k;
+        const float sj = nrm[j];
+        const size_t o = (size_t)rank_of[j] * k + i;
+        Ucol[o] = sj > 0.0f ? M[(size_t)j * LEN + i] / sj : 0.0f;
+        Vcol[o] = V[(size_t)j * LEN + i];
+    }
+}
+
 bool alloc_f(float **p, size_t count) {
     if (cudaMalloc(reinterpret_cast<void **>(p), std::max<size_t>(count, 1) * sizeof(float)) != cudaSuccess) {
         cudaGetLastError();
@@ -496,6 +628,13 @@ SvdWorkspace *svd_workspace_create_sharded(int m, int n, int k, int niter, int s
         ws->lwork = std::max(1, std::max(l1, l2));
         ok = ok && alloc_f(&ws->solver_work, (size_t)ws->lwork);
     }
+    {
+        const char *e = getenv("BSQ_CORE_SVD");              // "cusolver": keep the library solver (A/B comparisons)
+        ws->own_core_svd = ws->k <= kJacobiMaxK && !(e && e[0] == 'c');
+    }
+    if (ok && ws->own_core_svd)
+        ok = cudaFuncSetAttribute(jacobi_svd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)jacobi_smem_bytes(ws->k)) == cudaSuccess;
     if (ok && ws->k <= kCholeskyBlockedMaxK)
         ok = cudaFuncSetAttribute(cholesky_inverse_blocked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)cholesky_blocked_smem_bytes(ws->k)) == cudaSuccess;
@@ -577,9 +716,13 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
                     ws->sm_count, st)) != cudaSuccess)
         return err;
     // The row-major C read as column-major is C^T = Vc S Uc^T: the solver's "U" is Vc, its "V" is Uc.
-    if (cusolverDnSgesvdj(ws->solver, CUSOLVER_EIG_MODE_VECTOR, 0, k, k, ws->core, k, d_S, ws->vc, k, ws->uc, k,
-                          ws->solver_work, ws->lwork, ws->dev_info, ws->svdj) != CUSOLVER_STATUS_SUCCESS)
+    if (ws->own_core_svd) {
+        jacobi_svd_kernel<<<1, 1024, jacobi_smem_bytes(k), st>>>(ws->core, k, d_S, ws->vc, ws->uc);
+        if ((err = cudaGetLastError()) != cudaSuccess) return err;
+    } else if (cusolverDnSgesvdj(ws->solver, CUSOLVER_EIG_MODE_VECTOR, 0, k, k, ws->core, k, d_S, ws->vc, k, ws->uc, k,
+                                 ws->solver_work, ws->lwork, ws->dev_info, ws->svdj) != CUSOLVER_STATUS_SUCCESS) {
         return cudaErrorUnknown;
+    }
     // W = (Q Vc) S (Q2 Uc)^T; both k x k factors are column-major, i.e. K-major B operands
     float *d_left = ws->transposed ? d_V : d_U;            // M x k factor
     float *d_right = ws->transposed ? d_U : d_V;           // N x k factor
