@@ -216,10 +216,13 @@ cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, c
         GemmArgs t{};
         t.A = A; t.B = B; t.M = M; t.N = N; t.K = K; t.lda = lda; t.ldb = ldb;
         t.kscale = kscale; t.minuend = minuend; t.ldm = ldm;
-        const int tiles_tc = (M + 127) / 128;
+        // N up to 256 is one tile; wider products (the reconstruction) are cut into 128-column tiles
+        t.n_tile = N <= 256 ? N : 128;
+        t.flag = minuend ? flag : nullptr;
+        const int tiles_tc = ((M + 127) / 128) * ((N + t.n_tile - 1) / t.n_tile);
         int splits_tc = 1;
-        const int slots = (N <= 128 ? 2 : 1) * sm_count;
-        if (workspace && tiles_tc < slots) {
+        const int slots = (t.n_tile <= 128 ? 2 : 1) * sm_count;
+        if (workspace && !minuend && !kscale && tiles_tc < slots) {
             const int max_by_k = max(1, K / 64);
             const int max_by_ws = (int)(workspace_bytes / ((size_t)M * N * sizeof(float)));
             splits_tc = max(1, min(slots / tiles_tc, min(max_by_k, max_by_ws)));

@@ -19,10 +19,12 @@ struct GemmArgs {
     const float *minuend;      // nullable (only without splits): C = minuend - acc
     long ldm;
     unsigned *flag;            // nullable: |= 1 when some |C| > FLT_EPSILON (with minuend)
+    int n_tile;                // tensor-core kernel: columns per CTA (a multiple of 16, <= 256); grid.y tiles N
 };
 
-// Tensor-core path: true if the shape qualifies (N a multiple of 16 up to 256, 16-byte aligned operands with
-// leading dimensions that are multiples of 4, no fused epilogue).  Launches with grid (M tiles, 1, splits).
+// Tensor-core path: true if the shape qualifies (N a multiple of 16, 16-byte aligned operands with leading
+// dimensions that are multiples of 4; the fused scale / minuend epilogue only without K splits).  Launches with
+// grid (M tiles, N tiles, splits).
 bool gemm_tc_eligible(const GemmArgs &g, bool a_kmajor, bool b_kmajor);
 cudaError_t gemm_tc_launch(const GemmArgs &g, bool a_kmajor, bool b_kmajor, unsigned *status, cudaStream_t stream);
 

@@ -163,6 +163,22 @@ struct Slot {
             it.v[j] = v;
         }
     }
+    // opA(i, kk) *= sc[kk] for the chunk whose first k sc points at (k_left of its TK values exist)
+    __device__ __forceinline__ void scale(Item &it, const float *sc, int k_left) const {
+        if (KMAJOR) {
+            float f[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) f[q] = kq * 4 + q < k_left ? sc[kq * 4 + q] : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { it.v[j].x *= f[0]; it.v[j].y *= f[1]; it.v[j].z *= f[2]; it.v[j].w *= f[3]; }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float f = kq * 4 + j < k_left ? sc[kq * 4 + j] : 0.0f;
+                it.v[j].x *= f; it.v[j].y *= f; it.v[j].z *= f; it.v[j].w *= f;
+            }
+        }
+    }
     __device__ __forceinline__ void store(const Item &it, float4 *hi, float4 *lo) const {
         if (KMAJOR) {
 #pragma unroll
@@ -190,7 +206,8 @@ __global__ void __launch_bounds__(NT) gemm_tc_kernel(GemmArgs g, unsigned *statu
     __shared__ unsigned tmem_base_slot;
     constexpr int ITEMS = NMAX / (NT - TM);                   // slots of B per serving thread: 1 (N <= 128) or 2
     const int tid = threadIdx.x, warp = tid >> 5;
-    const int N = g.N;                                        // multiple of 16, <= NMAX
+    const int n0 = blockIdx.y * g.n_tile;                     // this CTA's columns: n0 .. n0 + N
+    const int N = min(g.n_tile, g.N - n0);                    // multiple of 16, <= NMAX
     const int m0 = blockIdx.x * TM;
     const int k_begin = blockIdx.z * g.k_per_split;
     const int k_end = min(g.K, k_begin + g.k_per_split);
@@ -226,12 +243,13 @@ __global__ void __launch_bounds__(NT) gemm_tc_kernel(GemmArgs g, unsigned *statu
     Slot<B_KMAJOR> slot_b[ITEMS];
     slot_a.init(g.A, g.lda, g.M, m0, k_begin, TM, serves_a ? tid : TM);
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i) slot_b[i].init(g.B, g.ldb, N, 0, k_begin, N, serves_a ? N : tid - TM + i * (NT - TM));
+    for (int i = 0; i < ITEMS; ++i) slot_b[i].init(g.B, g.ldb, g.N, n0, k_begin, N, serves_a ? N : tid - TM + i * (NT - TM));
     Item regs[DEPTH][ITEMS];
     auto load_chunk = [&](Item(&r)[ITEMS], int c, int k_left) {
         if (k_left >= TK) {
             if (serves_a) {
                 slot_a.load(r[0], c);
+                if (g.kscale) slot_a.scale(r[0], g.kscale + k_begin + c * TK, TK);
             } else {
 #pragma unroll
                 for (int i = 0; i < ITEMS; ++i)
@@ -239,6 +257,7 @@ __global__ void __launch_bounds__(NT) gemm_tc_kernel(GemmArgs g, unsigned *statu
             }
         } else if (serves_a) {
             slot_a.load_checked(r[0], c, k_left);
+            if (g.kscale) slot_a.scale(r[0], g.kscale + k_begin + c * TK, k_left);
         } else {
 #pragma unroll
             for (int i = 0; i < ITEMS; ++i)
@@ -306,6 +325,7 @@ __global__ void __launch_bounds__(NT) gemm_tc_kernel(GemmArgs g, unsigned *statu
     const int row = m0 + (warp & 3) * 32 + (tid & 31);
     const int half = (N / 16 + 1) / 2 * 16;                  // columns of the lower half, a multiple of 16
     const int c_begin = warp < 4 ? 0 : half, c_end = warp < 4 ? half : N;
+    bool any = false;
     if (ok) {
         for (int c0 = c_begin; c0 < c_end; c0 += 16) {
             unsigned r[16], q[16];
@@ -321,14 +341,28 @@ __global__ void __launch_bounds__(NT) gemm_tc_kernel(GemmArgs g, unsigned *statu
                 for (int j = 0; j < 16; ++j) r[j] = 0u;
             }
             if (row < g.M) {
-                float4 *dst = reinterpret_cast<float4 *>(C + (long)row * g.ldc + c0);
+                float4 *dst = reinterpret_cast<float4 *>(C + (long)row * g.ldc + n0 + c0);
+                if (g.minuend) {                             // C = minuend - product, note whether anything is left
+                    const float4 *mn = reinterpret_cast<const float4 *>(g.minuend + (long)row * g.ldm + n0 + c0);
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
-                                         __uint_as_float(r[4 * j + 3]));
+                    for (int j = 0; j < 4; ++j) {
+                        const float4 m4 = mn[j];
+                        const float4 o = make_float4(__fsub_rn(m4.x, __uint_as_float(r[4 * j])), __fsub_rn(m4.y, __uint_as_float(r[4 * j + 1])),
+                                                     __fsub_rn(m4.z, __uint_as_float(r[4 * j + 2])), __fsub_rn(m4.w, __uint_as_float(r[4 * j + 3])));
+                        any |= fabsf(o.x) > 1.1920928955078125e-07f || fabsf(o.y) > 1.1920928955078125e-07f ||
+                               fabsf(o.z) > 1.1920928955078125e-07f || fabsf(o.w) > 1.1920928955078125e-07f;
+                        dst[j] = o;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                                             __uint_as_float(r[4 * j + 3]));
+                }
             }
         }
     }
+    if (g.flag && __any_sync(0xffffffffu, any) && (tid & 31) == 0) atomicOr(g.flag, 1u);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) {
@@ -346,10 +380,10 @@ size_t tc_smem_bytes(int N) {
 
 template <bool AK, bool BK, int NMAX>
 cudaError_t launch(const GemmArgs &g, unsigned *status, cudaStream_t stream) {
-    const size_t smem = tc_smem_bytes(g.N);
+    const size_t smem = tc_smem_bytes(g.n_tile);
     cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<AK, BK, NMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return err;
-    dim3 grid((g.M + TM - 1) / TM, 1, g.splits);
+    dim3 grid((g.M + TM - 1) / TM, (g.N + g.n_tile - 1) / g.n_tile, g.splits);
     gemm_tc_kernel<AK, BK, NMAX><<<grid, NT, smem, stream>>>(g, status);
     return cudaGetLastError();
 }
@@ -359,18 +393,19 @@ cudaError_t launch(const GemmArgs &g, unsigned *status, cudaStream_t stream) {
 bool gemm_tc_eligible(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
     (void)a_kmajor;
     (void)b_kmajor;
-    if (g.N < 16 || g.N > 256 || g.N % 16 != 0) return false;
-    if (g.kscale || g.minuend) return false;
+    if (g.N < 16 || g.N % 16 != 0 || g.n_tile < 16 || g.n_tile > 256 || g.n_tile % 16 != 0) return false;
+    if ((g.kscale || g.minuend) && g.splits != 1) return false;
     if (g.lda % 4 != 0 || g.ldb % 4 != 0 || g.ldc % 4 != 0) return false;
     if ((reinterpret_cast<uintptr_t>(g.A) | reinterpret_cast<uintptr_t>(g.B) | reinterpret_cast<uintptr_t>(g.C)) % 16 != 0)
         return false;
+    if (g.minuend && (g.ldm % 4 != 0 || reinterpret_cast<uintptr_t>(g.minuend) % 16 != 0)) return false;
     if (g.k_per_split % TK != 0) return false;
     return g.M >= TM && g.K >= 4 * TK;
 }
 
 cudaError_t gemm_tc_launch(const GemmArgs &g, bool a_kmajor, bool b_kmajor, unsigned *status, cudaStream_t stream) {
 #define BSQ_TC(AK, BK)                                                                  \
-    (g.N <= 128 ? launch<AK, BK, 128>(g, status, stream) : launch<AK, BK, 256>(g, status, stream))
+    (g.n_tile <= 128 ? launch<AK, BK, 128>(g, status, stream) : launch<AK, BK, 256>(g, status, stream))
     if (a_kmajor && b_kmajor) return BSQ_TC(true, true);
     if (a_kmajor) return BSQ_TC(true, false);
     if (b_kmajor) return BSQ_TC(false, true);

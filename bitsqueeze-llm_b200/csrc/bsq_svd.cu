@@ -249,17 +249,35 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const fl
     float *dinv = tmp + (size_t)nb * kCB * kCB;            // 1 / R(i, i)
     float *red = dinv + nb * kCB;                          // 32 + 1
     const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
-    // load, padded with an identity; the part of a diagonal block below the diagonal is never read
+    // load, padded with an identity; the part of a diagonal block below the diagonal is never read.
+    // Four elements per thread and trip, so that four global loads are in flight at a time.
     float md = 0.0f;
-    for (int e = tid; e < nbt * kCB * kCB; e += nt) {
-        const int b = e / (kCB * kCB), w = e % (kCB * kCB);
-        int I = 0, rem = b;
-        while (rem >= nb - I) { rem -= nb - I; ++I; }      // block (I, I + rem)
-        const int i = I * kCB + w / kCB, c = (I + rem) * kCB + w % kCB;
-        float v = (i == c) ? 1.0f : 0.0f;
-        if (i < k && c < k) v = G[(size_t)i * k + c];
-        blocks[e] = v;
-        if (i == c && i < k) md = fmaxf(md, v);
+    for (int e0 = tid; e0 < nbt * kCB * kCB; e0 += 4 * nt) {
+        float v[4];
+        int pos[4];
+        bool diag[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int e = e0 + u * nt;
+            pos[u] = -1;
+            diag[u] = false;
+            v[u] = 0.0f;
+            if (e < nbt * kCB * kCB) {
+                const int b = e / (kCB * kCB), w = e % (kCB * kCB);
+                int I = 0, rem = b;
+                while (rem >= nb - I) { rem -= nb - I; ++I; }      // block (I, I + rem)
+                const int i = I * kCB + w / kCB, c = (I + rem) * kCB + w % kCB;
+                pos[u] = e;
+                diag[u] = i == c && i < k;
+                v[u] = (i == c) ? 1.0f : 0.0f;
+                if (i < k && c < k) v[u] = G[(size_t)i * k + c];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (pos[u] >= 0) blocks[pos[u]] = v[u];
+            if (diag[u]) md = fmaxf(md, v[u]);
+        }
     }
     for (int d = 16; d > 0; d >>= 1) md = fmaxf(md, __shfl_xor_sync(0xffffffffu, md, d));
     if (lane == 0) red[warp] = md;
@@ -419,10 +437,21 @@ __global__ void __launch_bounds__(1024) jacobi_svd_kernel(const float *__restric
     const int tid = threadIdx.x, nt = blockDim.x;
     const int slot = tid >> 4, l = tid & 15;                  // 16 lanes per pair, 64 pair slots
     const int F4 = LEN / 64;                                  // float4 per lane and column
-    for (int e = tid; e < kp * LEN; e += nt) {
-        const int j = e / LEN, i = e % LEN;
-        M[e] = (j < k && i < k) ? C[(size_t)j * k + i] : 0.0f;
-        V[e] = (i == j && j < k) ? 1.0f : 0.0f;
+    for (int e0 = tid; e0 < kp * LEN; e0 += 4 * nt) {        // four global loads in flight per thread
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int e = e0 + u * nt, j = e / LEN, i = e % LEN;
+            v[u] = (e < kp * LEN && j < k && i < k) ? C[(size_t)j * k + i] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int e = e0 + u * nt, j = e / LEN, i = e % LEN;
+            if (e < kp * LEN) {
+                M[e] = v[u];
+                V[e] = (i == j && j < k) ? 1.0f : 0.0f;
+            }
+        }
     }
     __syncthreads();
     const float tol = sqrtf((float)LEN) * 5.9604645e-08f;
