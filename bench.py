@@ -7,9 +7,10 @@ Workload (BASELINE.json configs[1]): one 4096 x 4096 FP32 activation matrix per 
 seeded synthetic.  A step is one pass of the hot path (per-row outlier separation fused with the
 NF4_DQ quantiser) over one matrix.
 
-  value  FP32-input GB/s of the device stages with the input resident in HBM (CUDA events on the
-         launching stream, barrier + synchronize on both sides, max over ranks).  Successive steps
-         rotate over 4 different input matrices (256 MiB > the 126 MB L2), so no step finds its
+  value  FP32-input GB/s of the device stages with the input resident in HBM (CUDA events, barrier +
+         synchronize on both sides, max over ranks).  Matrices are independent, so the job keeps two of
+         them in flight on two streams; the single-stream time per step is reported in config.  Successive
+         steps rotate over 4 different input matrices (256 MiB > the 126 MB L2), so no step finds its
          input in L2 from the step before.
   e2e    the same metric through the public bitsqz_llm_compress call with a pinned HOST matrix:
          host->device copy of the input and device->host copy of the packed object inside the
@@ -41,6 +42,7 @@ import __graft_entry__ as entry  # noqa: E402
 
 ROWS, COLS, OUTLIER_RATIO, METHOD = 4096, 4096, 0.01, 10
 NBUF = 4
+INFLIGHT = 2            # matrices in flight in the device-stage loop, one stream each
 # dram__bytes_read.sum + dram__bytes_write.sum of one frontend_select_kernel launch on this workload, from the ncu
 # capture summarised in profiles/frontend_nf4dq_c2_4096x4096.md (67 174 400 + 502 272)
 NCU_TRAFFIC_SELECT = 67676672
@@ -298,44 +300,74 @@ def main():
     nb = n // 64
     host = [make_matrix(1000 * rank + i) for i in range(NBUF)]
     d_in = [torch.from_numpy(h).cuda() for h in host]
-    d_idx = torch.zeros((ROWS, k), dtype=torch.int16, device="cuda")
-    d_val = torch.zeros((ROWS, k), dtype=torch.float32, device="cuda")
-    d_dq = torch.zeros(4, dtype=torch.float32, device="cuda")
-    d_codes = torch.zeros(nb, dtype=torch.uint8, device="cuda")
-    d_data = torch.zeros(n // 2, dtype=torch.uint8, device="cuda")
-    d_scr = torch.zeros(L.bsq_frontend_scratch_bytes(ROWS, COLS), dtype=torch.uint8, device="cuda")
-    d_st = torch.zeros(4, dtype=torch.int32, device="cuda")
-    stream = torch.cuda.current_stream().cuda_stream
 
-    def stage(i):
-        rc = L.bsq_frontend_quantize(METHOD, d_in[i % NBUF].data_ptr(), ROWS, COLS, k, d_idx.data_ptr(), d_val.data_ptr(),
-                                     None, d_dq.data_ptr(), d_codes.data_ptr(), d_data.data_ptr(), d_scr.data_ptr(),
-                                     d_st.data_ptr(), stream)
+    class Outputs:
+        """Device outputs and scratch of one matrix in flight."""
+        def __init__(self):
+            self.idx = torch.zeros((ROWS, k), dtype=torch.int16, device="cuda")
+            self.val = torch.zeros((ROWS, k), dtype=torch.float32, device="cuda")
+            self.dq = torch.zeros(4, dtype=torch.float32, device="cuda")
+            self.codes = torch.zeros(nb, dtype=torch.uint8, device="cuda")
+            self.data = torch.zeros(n // 2, dtype=torch.uint8, device="cuda")
+            self.scr = torch.zeros(L.bsq_frontend_scratch_bytes(ROWS, COLS), dtype=torch.uint8, device="cuda")
+            self.st = torch.zeros(4, dtype=torch.int32, device="cuda")
+
+    # Independent matrices are the unit of this workload, so the job keeps INFLIGHT of them in flight, each on a
+    # stream of its own with its own outputs (the stage entry point takes a stream): the tail of one matrix's
+    # kernels overlaps the head of the next one's.  One stream alone is measured too (single_stream_ms_per_step).
+    outs = [Outputs() for _ in range(INFLIGHT)]
+    streams = [torch.cuda.Stream() for _ in range(INFLIGHT)]
+    main_stream = torch.cuda.current_stream()
+    o0 = outs[0]
+    d_idx, d_val, d_dq, d_codes, d_data, d_scr, d_st = o0.idx, o0.val, o0.dq, o0.codes, o0.data, o0.scr, o0.st
+    stream = main_stream.cuda_stream
+
+    def stage(i, lanes=INFLIGHT):
+        o = outs[i % lanes]
+        st = streams[i % lanes].cuda_stream if lanes > 1 else stream
+        rc = L.bsq_frontend_quantize(METHOD, d_in[i % NBUF].data_ptr(), ROWS, COLS, k, o.idx.data_ptr(), o.val.data_ptr(),
+                                     None, o.dq.data_ptr(), o.codes.data_ptr(), o.data.data_ptr(), o.scr.data_ptr(),
+                                     o.st.data_ptr(), st)
         if rc != 0:
             raise RuntimeError("bsq_frontend_quantize failed")
+
+    def timed_stage_loop(lanes):
+        """K steps, CUDA events on the main stream around them; the other streams are fenced by events on both sides."""
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(main_stream)
+        if lanes > 1:
+            for s_ in streams[:lanes]:
+                s_.wait_event(e0)
+        for i in range(args.steps):
+            stage(i, lanes)
+        if lanes > 1:
+            for s_ in streams[:lanes]:
+                main_stream.wait_stream(s_)
+        e1.record(main_stream)
+        barrier()
+        return e0.elapsed_time(e1)
 
     # ---- device-stage throughput ----
     for i in range(args.warmup):
         stage(i)
+    for i in range(args.warmup):
+        stage(i, 1)
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for i in range(args.steps):
-        stage(i)
-    e1.record()
-    barrier()
-    ms_total = e0.elapsed_time(e1)
     if args.stage_only:
+        ms_total = timed_stage_loop(1)
         if rank == 0:
             sampler.stop()
             print(json.dumps({"stage_only": True, "ms_per_step": ms_total / args.steps}))
         return
-    if int(d_st[0]) != 0:
-        raise RuntimeError("kernel status word set: %d" % int(d_st[0]))
+    ms_total = timed_stage_loop(INFLIGHT)
+    ms_single = timed_stage_loop(1)
+    for o in outs:
+        if int(o.st[0]) != 0:
+            raise RuntimeError("kernel status word set: %d" % int(o.st[0]))
 
     # ---- per-pass durations for the roofline (events between the two kernels) ----
     ms_pass = (C.c_float * 2)()
@@ -375,10 +407,10 @@ def main():
 
     # ---- decompress (device stages: NF4_DQ dequantise + outlier scatter-add), reported beside ----
     d_out = torch.zeros((ROWS, COLS), dtype=torch.float32, device="cuda")
-    outs = [torch.zeros((ROWS, COLS), dtype=torch.float32, device="cuda") for _ in range(NBUF)]
+    douts = [torch.zeros((ROWS, COLS), dtype=torch.float32, device="cuda") for _ in range(NBUF)]
 
     def dstage(i):
-        o = outs[i % NBUF]
+        o = douts[i % NBUF]
         L.bsq_nf4dq_dequantize(d_dq.data_ptr(), d_codes.data_ptr(), d_data.data_ptr(), n, o.data_ptr(), stream)
         L.bsq_topk_apply(d_idx.data_ptr(), d_val.data_ptr(), ROWS, COLS, k, o.data_ptr(), d_st.data_ptr(), stream)
     for i in range(args.warmup):
@@ -398,7 +430,7 @@ def main():
     spec = importlib.util.spec_from_file_location("bsq_shard", os.path.join(entry.PKG_DIR, "shard.py"))
     shard = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(shard)
-    ms_total, e2e_ms, ms_dec, ms_p1, ms_p2 = shard.max_over_ranks([ms_total, e2e_s * 1e3, ms_dec, ms_p1, ms_p2], device="cuda")
+    ms_total, e2e_ms, ms_dec, ms_p1, ms_p2, ms_single = shard.max_over_ranks([ms_total, e2e_s * 1e3, ms_dec, ms_p1, ms_p2, ms_single], device="cuda")
 
     if rank == 0:
         in_bytes = n * 4
@@ -417,7 +449,9 @@ def main():
             "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": "configs[1]: 4096x4096 FP32 device matrix, outlier_topk=0.01 (k=41/row), NF4_DQ, no SVD",
-                       "rows": ROWS, "cols": COLS, "k": int(k), "parallelism": f"independent matrices x{world}",
+                       "rows": ROWS, "cols": COLS, "k": int(k),
+                       "parallelism": f"independent matrices x{world} GPU(s), {INFLIGHT} in flight per GPU on separate streams",
+                       "single_stream_ms_per_step": ms_single / args.steps,
                        "l2": f"inputs rotate over {NBUF} x 64 MiB matrices (256 MiB > 126 MB L2)"},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": int(packed_size),
                     "api": "bitsqz_llm_compress, BITSQZ_LLM_INPUT_HOST, pinned input"},
