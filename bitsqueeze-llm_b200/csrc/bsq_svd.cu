@@ -418,7 +418,7 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const fl
 //   out: M = U diag(S) V^T with S descending; U and V column-major k x k
 // Column pairs (p, q) are rotated until all columns of M V are orthogonal to tol (LAPACK's sgesvj criterion,
 // |m_p . m_q| <= tol |m_p| |m_q|, tol = sqrt(len) eps); the k / 2 pairs of a round are disjoint (round-robin
-// schedule), 16 lanes serve a pair, a CTA barrier separates the rounds.  Squared column norms are carried along
+// schedule), 8 lanes serve a pair, a CTA barrier separates the rounds.  Squared column norms are carried along
 // through the rotations and recomputed exactly at the start of every sweep.  At the end S(j) = |column j|,
 // U(:, j) = column j / S(j) (zero for S(j) = 0), and a rank by counting puts S in descending order.
 constexpr int kJacobiMaxK = 128;
@@ -428,15 +428,15 @@ __host__ __device__ constexpr size_t jacobi_smem_bytes(int k) {
     return ((size_t)2 * ((k + 1) & ~1) * jacobi_len(k) + 2 * (size_t)((k + 1) & ~1) + 64) * sizeof(float);
 }
 
-__global__ void __launch_bounds__(1024) jacobi_svd_kernel(const float *__restrict__ C, int k, float *__restrict__ S,
-                                                          float *__restrict__ Ucol, float *__restrict__ Vcol) {
+__global__ void __launch_bounds__(512) jacobi_svd_kernel(const float *__restrict__ C, int k, float *__restrict__ S,
+                                                         float *__restrict__ Ucol, float *__restrict__ Vcol) {
     extern __shared__ __align__(16) float sm[];
     const int LEN = jacobi_len(k), kp = (k + 1) & ~1, npairs = kp / 2;
     float *M = sm, *V = M + (size_t)kp * LEN, *nrm = V + (size_t)kp * LEN;
     int *rank_of = reinterpret_cast<int *>(nrm + kp);
     const int tid = threadIdx.x, nt = blockDim.x;
-    const int slot = tid >> 4, l = tid & 15;                  // 16 lanes per pair, 64 pair slots
-    const int F4 = LEN / 64;                                  // float4 per lane and column
+    const int slot = tid >> 3, l = tid & 7;                   // 8 lanes per pair, 64 pair slots
+    const int F4 = LEN / 32;                                  // float4 per lane and column: 2 or 4
     for (int e0 = tid; e0 < kp * LEN; e0 += 4 * nt) {        // four global loads in flight per thread
         float v[4];
 #pragma unroll
@@ -454,23 +454,25 @@ __global__ void __launch_bounds__(1024) jacobi_svd_kernel(const float *__restric
         }
     }
     __syncthreads();
-    const float tol = sqrtf((float)LEN) * 5.9604645e-08f;
-    auto dot16 = [&](float x) {                               // sum over the 16 lanes of a pair slot
-        x += __shfl_xor_sync(0xffffffffu, x, 8, 16);
-        x += __shfl_xor_sync(0xffffffffu, x, 4, 16);
-        x += __shfl_xor_sync(0xffffffffu, x, 2, 16);
-        x += __shfl_xor_sync(0xffffffffu, x, 1, 16);
+    const float tol = sqrtf((float)LEN) * 5.9604645e-08f, tol2 = tol * tol;
+    auto sum8 = [&](float x) {                                // sum over the 8 lanes of a pair slot
+        x += __shfl_xor_sync(0xffffffffu, x, 4, 8);
+        x += __shfl_xor_sync(0xffffffffu, x, 2, 8);
+        x += __shfl_xor_sync(0xffffffffu, x, 1, 8);
         return x;
     };
+    auto norm2 = [&](int j) {
+        float acc = 0.0f;
+        for (int f = 0; f < F4; ++f) {
+            const float4 a = reinterpret_cast<const float4 *>(M + (size_t)j * LEN)[f * 8 + l];
+            acc += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        }
+        return sum8(acc);
+    };
     for (int sweep = 0; sweep < kJacobiMaxSweeps; ++sweep) {
-        for (int j = slot; j < kp; j += nt / 16) {            // exact squared norms
-            float acc = 0.0f;
-            for (int f = 0; f < F4; ++f) {
-                const float4 a = reinterpret_cast<const float4 *>(M + (size_t)j * LEN)[f * 16 + l];
-                acc += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
-            }
-            acc = dot16(acc);
-            if (l == 0) nrm[j] = acc;
+        for (int j = slot; j < kp; j += nt / 8) {             // exact squared norms
+            const float a = norm2(j);
+            if (l == 0) nrm[j] = a;
         }
         __syncthreads();
         bool rotated = false;
@@ -482,33 +484,34 @@ __global__ void __launch_bounds__(1024) jacobi_svd_kernel(const float *__restric
                 else { p = (r + slot) % (kp - 1); q = (r + kp - 1 - slot) % (kp - 1); }
             }
             float4 *mp = reinterpret_cast<float4 *>(M + (size_t)p * LEN), *mq = reinterpret_cast<float4 *>(M + (size_t)q * LEN);
-            float4 ap[2], aq[2];
+            float4 ap[4], aq[4];
             float g = 0.0f;
 #pragma unroll
-            for (int f = 0; f < 2; ++f) {
+            for (int f = 0; f < 4; ++f) {
                 if (f < F4) {
-                    ap[f] = mp[f * 16 + l];
-                    aq[f] = mq[f * 16 + l];
+                    ap[f] = mp[f * 8 + l];
+                    aq[f] = mq[f * 8 + l];
                     g += ap[f].x * aq[f].x + ap[f].y * aq[f].y + ap[f].z * aq[f].z + ap[f].w * aq[f].w;
                 }
             }
-            g = dot16(g);
+            g = sum8(g);
             const float alpha = nrm[p], beta = nrm[q];
-            if (active && alpha > 0.0f && beta > 0.0f && fabsf(g) > tol * sqrtf(alpha) * sqrtf(beta)) {
+            // |m_p . m_q| > tol |m_p| |m_q|, compared in squares
+            if (active && alpha > 0.0f && beta > 0.0f && g * g > tol2 * alpha * beta) {
                 const float zeta = (beta - alpha) / (2.0f * g);
                 // 1 / (2 zeta) once zeta^2 would overflow: the rotation is then too small to change anything
                 const float t = fabsf(zeta) > 1.0e8f ? 0.5f / zeta : copysignf(1.0f, zeta) / (fabsf(zeta) + sqrtf(1.0f + zeta * zeta));
                 const float c = rsqrtf(1.0f + t * t), sn = c * t;
                 float4 *vp = reinterpret_cast<float4 *>(V + (size_t)p * LEN), *vq = reinterpret_cast<float4 *>(V + (size_t)q * LEN);
 #pragma unroll
-                for (int f = 0; f < 2; ++f) {
+                for (int f = 0; f < 4; ++f) {
                     if (f < F4) {
                         const float4 x = ap[f], y = aq[f];
-                        mp[f * 16 + l] = make_float4(c * x.x - sn * y.x, c * x.y - sn * y.y, c * x.z - sn * y.z, c * x.w - sn * y.w);
-                        mq[f * 16 + l] = make_float4(sn * x.x + c * y.x, sn * x.y + c * y.y, sn * x.z + c * y.z, sn * x.w + c * y.w);
-                        const float4 u = vp[f * 16 + l], w = vq[f * 16 + l];
-                        vp[f * 16 + l] = make_float4(c * u.x - sn * w.x, c * u.y - sn * w.y, c * u.z - sn * w.z, c * u.w - sn * w.w);
-                        vq[f * 16 + l] = make_float4(sn * u.x + c * w.x, sn * u.y + c * w.y, sn * u.z + c * w.z, sn * u.w + c * w.w);
+                        mp[f * 8 + l] = make_float4(c * x.x - sn * y.x, c * x.y - sn * y.y, c * x.z - sn * y.z, c * x.w - sn * y.w);
+                        mq[f * 8 + l] = make_float4(sn * x.x + c * y.x, sn * x.y + c * y.y, sn * x.z + c * y.z, sn * x.w + c * y.w);
+                        const float4 u = vp[f * 8 + l], w = vq[f * 8 + l];
+                        vp[f * 8 + l] = make_float4(c * u.x - sn * w.x, c * u.y - sn * w.y, c * u.z - sn * w.z, c * u.w - sn * w.w);
+                        vq[f * 8 + l] = make_float4(sn * u.x + c * w.x, sn * u.y + c * w.y, sn * u.z + c * w.z, sn * u.w + c * w.w);
                     }
                 }
                 if (l == 0) {
@@ -522,14 +525,9 @@ __global__ void __launch_bounds__(1024) jacobi_svd_kernel(const float *__restric
         if (!__syncthreads_or(rotated)) break;
     }
     // singular values, order, output
-    for (int j = slot; j < kp; j += nt / 16) {
-        float acc = 0.0f;
-        for (int f = 0; f < F4; ++f) {
-            const float4 a = reinterpret_cast<const float4 *>(M + (size_t)j * LEN)[f * 16 + l];
-            acc += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
-        }
-        acc = dot16(acc);
-        if (l == 0) nrm[j] = sqrtf(acc);
+    for (int j = slot; j < kp; j += nt / 8) {
+        const float a = norm2(j);
+        if (l == 0) nrm[j] = sqrtf(a);
     }
     __syncthreads();
     for (int j = tid; j < k; j += nt) {
@@ -648,6 +646,13 @@ SvdWorkspace *svd_workspace_create_sharded(int m, int n, int k, int niter, int s
     ok = ok && curandCreateGenerator(&ws->rng, CURAND_RNG_PSEUDO_DEFAULT) == CURAND_STATUS_SUCCESS;
     ok = ok && cusolverDnCreate(&ws->solver) == CUSOLVER_STATUS_SUCCESS;
     ok = ok && cusolverDnCreateGesvdjInfo(&ws->svdj) == CUSOLVER_STATUS_SUCCESS;
+    {
+        // Jacobi stops when the columns are orthogonal to this tolerance; the library's default is machine epsilon.
+        // The factors only have to carry FP32 products to ~1e-6, and every sweep over a 256 x 256 core costs 0.4 ms.
+        double tol = 1.0e-6;
+        if (const char *e = getenv("BSQ_CORE_SVD_TOL")) tol = atof(e);
+        ok = ok && cusolverDnXgesvdjSetTolerance(ws->svdj, tol) == CUSOLVER_STATUS_SUCCESS;
+    }
     if (ok) {
         int l1 = 0, l2 = 0;
         ok = cusolverDnSsyevd_bufferSize(ws->solver, CUSOLVER_EIG_MODE_VECTOR, CUBLAS_FILL_MODE_LOWER, ws->k, ws->g, ws->k,
@@ -746,7 +751,7 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
         return err;
     // The row-major C read as column-major is C^T = Vc S Uc^T: the solver's "U" is Vc, its "V" is Uc.
     if (ws->own_core_svd) {
-        jacobi_svd_kernel<<<1, 1024, jacobi_smem_bytes(k), st>>>(ws->core, k, d_S, ws->vc, ws->uc);
+        jacobi_svd_kernel<<<1, 512, jacobi_smem_bytes(k), st>>>(ws->core, k, d_S, ws->vc, ws->uc);
         if ((err = cudaGetLastError()) != cudaSuccess) return err;
     } else if (cusolverDnSgesvdj(ws->solver, CUSOLVER_EIG_MODE_VECTOR, 0, k, k, ws->core, k, d_S, ws->vc, k, ws->uc, k,
                                  ws->solver_work, ws->lwork, ws->dev_info, ws->svdj) != CUSOLVER_STATUS_SUCCESS) {
