@@ -22,6 +22,7 @@
 // seeded per call, column-major N x k.
 #include "bsq_internal.hpp"
 
+#include <cooperative_groups.h>
 #include <curand.h>
 #include <cusolverDn.h>
 
@@ -421,7 +422,8 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const fl
 // schedule), 8 lanes serve a pair, a CTA barrier separates the rounds.  Squared column norms are carried along
 // through the rotations and recomputed exactly at the start of every sweep.  At the end S(j) = |column j|,
 // U(:, j) = column j / S(j) (zero for S(j) = 0), and a rank by counting puts S in descending order.
-constexpr int kJacobiMaxK = 128;
+constexpr int kJacobiMaxK = 128;              // what the one-CTA kernel can hold
+constexpr int kJacobiSingleMaxK = 64;         // what it is used for: above, the cluster kernel is faster
 constexpr int kJacobiMaxSweeps = 30;
 __host__ __device__ constexpr int jacobi_len(int k) { return k <= 64 ? 64 : 128; }
 __host__ __device__ constexpr size_t jacobi_smem_bytes(int k) {
@@ -461,18 +463,21 @@ __global__ void __launch_bounds__(512) jacobi_svd_kernel(const float *__restrict
         x += __shfl_xor_sync(0xffffffffu, x, 1, 8);
         return x;
     };
+    // squared norm of column j; every lane of a warp calls it together (columns past the end count as zero)
     auto norm2 = [&](int j) {
         float acc = 0.0f;
-        for (int f = 0; f < F4; ++f) {
-            const float4 a = reinterpret_cast<const float4 *>(M + (size_t)j * LEN)[f * 8 + l];
-            acc += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        if (j < kp) {
+            for (int f = 0; f < F4; ++f) {
+                const float4 a = reinterpret_cast<const float4 *>(M + (size_t)j * LEN)[f * 8 + l];
+                acc += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+            }
         }
         return sum8(acc);
     };
     for (int sweep = 0; sweep < kJacobiMaxSweeps; ++sweep) {
-        for (int j = slot; j < kp; j += nt / 8) {             // exact squared norms
-            const float a = norm2(j);
-            if (l == 0) nrm[j] = a;
+        for (int j0 = 0; j0 < kp; j0 += nt / 8) {             // exact squared norms (uniform trip count: shuffles inside)
+            const float a = norm2(j0 + slot);
+            if (l == 0 && j0 + slot < kp) nrm[j0 + slot] = a;
         }
         __syncthreads();
         bool rotated = false;
@@ -525,9 +530,9 @@ __global__ void __launch_bounds__(512) jacobi_svd_kernel(const float *__restrict
         if (!__syncthreads_or(rotated)) break;
     }
     // singular values, order, output
-    for (int j = slot; j < kp; j += nt / 8) {
-        const float a = norm2(j);
-        if (l == 0) nrm[j] = sqrtf(a);
+    for (int j0 = 0; j0 < kp; j0 += nt / 8) {
+        const float a = norm2(j0 + slot);
+        if (l == 0 && j0 + slot < kp) nrm[j0 + slot] = sqrtf(a);
     }
     __syncthreads();
     for (int j = tid; j < k; j += nt) {
@@ -548,6 +553,174 @@ __global__ void __launch_bounds__(512) jacobi_svd_kernel(const float *__restrict
         Ucol[o] = sj > 0.0f ? M[(size_t)j * LEN + i] / sj : 0.0f;
         Vcol[o] = V[(size_t)j * LEN + i];
     }
+}
+
+// The same Jacobi iteration for larger cores, up to kJacobiClusterMaxK (two 256 x 256 matrices do not fit one SM's
+// shared memory, and already at 128 x 128 one SM's shared-memory bandwidth is the limit): a thread-block cluster of
+// 8 CTAs, each holding a slice of LEN / 8 rows of every column of M and V.  A column
+// pair's dot product is the sum of the eight slices' partial products: every CTA stores its partials into the
+// shared memory of all eight (distributed shared memory), one cluster barrier later every CTA adds them in the
+// same order, so all of them see bit-identical values, take identical decisions and rotate their own slices with
+// identical angles.  Control flow is the same in all CTAs by construction (same data, same arithmetic), which is
+// what the hardware cluster barrier needs; the sweep count is bounded.
+constexpr int kJacobiClusterMaxK = 256;
+constexpr int kJcCtas = 8;                                   // 16 measured slower: the barrier and the remote stores grow
+__host__ __device__ constexpr int jacobi_cluster_len(int k) { return k <= 128 ? 128 : 256; }     // padded column length
+__host__ __device__ constexpr size_t jacobi_cluster_smem_bytes(int k) {
+    // M and V slices, norms, two rounds of kJcCtas x LEN / 2 partial products, kJcCtas x LEN partial norms, ranks
+    return ((size_t)2 * ((k + 1) & ~1) * (jacobi_cluster_len(k) / kJcCtas) + ((k + 1) & ~1) + kJcCtas * jacobi_cluster_len(k) +
+            kJcCtas * jacobi_cluster_len(k) + jacobi_cluster_len(k) + 64) * sizeof(float);
+}
+
+template <int kJcLen>
+__global__ void __launch_bounds__(2 * kJcLen) jacobi_svd_cluster_kernel(const float *__restrict__ C, int k, float *__restrict__ S,
+                                                                        float *__restrict__ Ucol, float *__restrict__ Vcol) {
+    constexpr int kJcRows = kJcLen / kJcCtas, kJcF4 = kJcRows / 16;      // rows per CTA; float4 per lane and column
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned cr = cluster.block_rank();                 // this CTA holds rows cr * kJcRows .. + kJcRows - 1
+    extern __shared__ __align__(16) float sm[];
+    const int kp = (k + 1) & ~1, npairs = kp / 2;
+    float *M = sm, *V = M + (size_t)kp * kJcRows, *nrm = V + (size_t)kp * kJcRows;
+    float *part = nrm + kp;                                   // [2][4][128]
+    float *npart = part + 2 * kJcCtas * (kJcLen / 2);         // [4][256]
+    int *rank_of = reinterpret_cast<int *>(npart + kJcCtas * kJcLen);
+    float *part_at[kJcCtas], *npart_at[kJcCtas];              // the same arrays in every CTA of the cluster
+#pragma unroll
+    for (int d = 0; d < kJcCtas; ++d) {
+        part_at[d] = cluster.map_shared_rank(part, d);
+        npart_at[d] = cluster.map_shared_rank(npart, d);
+    }
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const int slot = tid >> 2, l = tid & 3;                   // 4 lanes per pair, 128 pair slots, kJcF4 float4 per lane and column
+    const int row0 = cr * kJcRows;
+    for (int e0 = tid; e0 < kp * kJcRows; e0 += 4 * nt) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int e = e0 + u * nt, j = e / kJcRows, i = row0 + e % kJcRows;
+            v[u] = (e < kp * kJcRows && j < k && i < k) ? C[(size_t)j * k + i] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int e = e0 + u * nt, j = e / kJcRows, i = row0 + e % kJcRows;
+            if (e < kp * kJcRows) {
+                M[e] = v[u];
+                V[e] = (i == j && j < k) ? 1.0f : 0.0f;
+            }
+        }
+    }
+    __syncthreads();
+    const float tol = sqrtf((float)kJcLen) * 5.9604645e-08f, tol2 = tol * tol;
+    auto sum4 = [&](float x) {
+        x += __shfl_xor_sync(0xffffffffu, x, 2, 4);
+        x += __shfl_xor_sync(0xffffffffu, x, 1, 4);
+        return x;
+    };
+    // exact squared norms of all columns: partial over this CTA's rows, exchanged, added in CTA order
+    auto exact_norms = [&](bool root) {
+        for (int j0 = 0; j0 < kp; j0 += nt / 4) {             // uniform trip count: shuffles inside
+            const int j = j0 + slot;
+            float acc = 0.0f;
+            if (j < kp) {
+#pragma unroll
+                for (int f = 0; f < kJcF4; ++f) {
+                    const float4 a = reinterpret_cast<const float4 *>(M + (size_t)j * kJcRows)[f * 4 + l];
+                    acc += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+                }
+            }
+            acc = sum4(acc);
+            if (l == 0 && j < kp) {
+#pragma unroll
+                for (int d = 0; d < kJcCtas; ++d) npart_at[d][cr * kJcLen + j] = acc;
+            }
+        }
+        cluster.sync();
+        for (int j = tid; j < kp; j += nt) {
+            float a = 0.0f;
+#pragma unroll
+            for (int d = 0; d < kJcCtas; ++d) a += npart[d * kJcLen + j];
+            nrm[j] = root ? sqrtf(a) : a;
+        }
+        __syncthreads();
+    };
+    for (int sweep = 0; sweep < kJacobiMaxSweeps; ++sweep) {
+        exact_norms(false);
+        bool rotated = false;
+        for (int r = 0; r < kp - 1; ++r) {
+            const bool active = slot < npairs;
+            int p = 0, q = 0;
+            if (active) {
+                if (slot == 0) { p = kp - 1; q = r; }
+                else { p = (r + slot) % (kp - 1); q = (r + kp - 1 - slot) % (kp - 1); }
+            }
+            float4 *mp = reinterpret_cast<float4 *>(M + (size_t)p * kJcRows), *mq = reinterpret_cast<float4 *>(M + (size_t)q * kJcRows);
+            float4 ap[kJcF4], aq[kJcF4];
+            float g = 0.0f;
+#pragma unroll
+            for (int f = 0; f < kJcF4; ++f) {
+                ap[f] = mp[f * 4 + l];
+                aq[f] = mq[f * 4 + l];
+                g += ap[f].x * aq[f].x + ap[f].y * aq[f].y + ap[f].z * aq[f].z + ap[f].w * aq[f].w;
+            }
+            g = sum4(g);
+            const int par = r & 1;
+            if (l == 0) {
+#pragma unroll
+                for (int d = 0; d < kJcCtas; ++d) part_at[d][(par * kJcCtas + cr) * (kJcLen / 2) + slot] = g;
+            }
+            cluster.sync();                                   // partials of this round are everywhere
+            const float *pp = part + par * kJcCtas * (kJcLen / 2) + slot;
+            g = 0.0f;
+#pragma unroll
+            for (int d = 0; d < kJcCtas; ++d) g += pp[d * (kJcLen / 2)];
+            const float alpha = nrm[p], beta = nrm[q];
+            if (active && alpha > 0.0f && beta > 0.0f && g * g > tol2 * alpha * beta) {
+                const float zeta = (beta - alpha) / (2.0f * g);
+                const float t = fabsf(zeta) > 1.0e8f ? 0.5f / zeta : copysignf(1.0f, zeta) / (fabsf(zeta) + sqrtf(1.0f + zeta * zeta));
+                const float c = rsqrtf(1.0f + t * t), sn = c * t;
+                float4 *vp = reinterpret_cast<float4 *>(V + (size_t)p * kJcRows), *vq = reinterpret_cast<float4 *>(V + (size_t)q * kJcRows);
+#pragma unroll
+                for (int f = 0; f < kJcF4; ++f) {
+                    const float4 x = ap[f], y = aq[f];
+                    mp[f * 4 + l] = make_float4(c * x.x - sn * y.x, c * x.y - sn * y.y, c * x.z - sn * y.z, c * x.w - sn * y.w);
+                    mq[f * 4 + l] = make_float4(sn * x.x + c * y.x, sn * x.y + c * y.y, sn * x.z + c * y.z, sn * x.w + c * y.w);
+                    const float4 u = vp[f * 4 + l], w = vq[f * 4 + l];
+                    vp[f * 4 + l] = make_float4(c * u.x - sn * w.x, c * u.y - sn * w.y, c * u.z - sn * w.z, c * u.w - sn * w.w);
+                    vq[f * 4 + l] = make_float4(sn * u.x + c * w.x, sn * u.y + c * w.y, sn * u.z + c * w.z, sn * u.w + c * w.w);
+                }
+                if (l == 0) {
+                    nrm[p] = fmaxf(alpha - t * g, 0.0f);
+                    nrm[q] = beta + t * g;
+                }
+                rotated = rotated || sn != 0.0f;
+            }
+            __syncthreads();                                  // this CTA's slices are rotated before the next round reads them
+        }
+        if (!__syncthreads_or(rotated)) break;               // the same answer in every CTA: they rotated with the same numbers
+    }
+    exact_norms(true);                                        // nrm = singular values
+    for (int j = tid; j < k; j += nt) {
+        const float sj = nrm[j];
+        int rk = 0;
+        for (int i = 0; i < k; ++i) {
+            const float si = nrm[i];
+            rk += (si > sj || (si == sj && i < j)) ? 1 : 0;
+        }
+        rank_of[j] = rk;
+        if (cr == 0) S[rk] = sj;
+    }
+    __syncthreads();
+    for (int e = tid; e < k * kJcRows; e += nt) {
+        const int j = e / kJcRows, i = row0 + e % kJcRows;
+        if (i < k) {
+            const float sj = nrm[j];
+            const size_t o = (size_t)rank_of[j] * k + i;
+            Ucol[o] = sj > 0.0f ? M[e] / sj : 0.0f;
+            Vcol[o] = V[e];
+        }
+    }
+    cluster.sync();                                           // nobody leaves while a neighbour could still store into it
 }
 
 bool alloc_f(float **p, size_t count) {
@@ -664,11 +837,16 @@ SvdWorkspace *svd_workspace_create_sharded(int m, int n, int k, int niter, int s
     }
     {
         const char *e = getenv("BSQ_CORE_SVD");              // "cusolver": keep the library solver (A/B comparisons)
-        ws->own_core_svd = ws->k <= kJacobiMaxK && !(e && e[0] == 'c');
+        ws->own_core_svd = ws->k <= kJacobiClusterMaxK && !(e && e[0] == 'c');
     }
-    if (ok && ws->own_core_svd)
+    if (ok && ws->own_core_svd && ws->k <= kJacobiSingleMaxK)
         ok = cudaFuncSetAttribute(jacobi_svd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)jacobi_smem_bytes(ws->k)) == cudaSuccess;
+    if (ok && ws->own_core_svd && ws->k > kJacobiSingleMaxK)
+        ok = (ws->k <= 128 ? cudaFuncSetAttribute(jacobi_svd_cluster_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  (int)jacobi_cluster_smem_bytes(ws->k))
+                           : cudaFuncSetAttribute(jacobi_svd_cluster_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  (int)jacobi_cluster_smem_bytes(ws->k))) == cudaSuccess;
     if (ok && ws->k <= kCholeskyBlockedMaxK)
         ok = cudaFuncSetAttribute(cholesky_inverse_blocked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)cholesky_blocked_smem_bytes(ws->k)) == cudaSuccess;
@@ -750,7 +928,25 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
                     ws->sm_count, st)) != cudaSuccess)
         return err;
     // The row-major C read as column-major is C^T = Vc S Uc^T: the solver's "U" is Vc, its "V" is Uc.
-    if (ws->own_core_svd) {
+    if (ws->own_core_svd && k > kJacobiSingleMaxK) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(kJcCtas, 1, 1);
+        cfg.blockDim = dim3(2 * jacobi_cluster_len(k), 1, 1);
+        cfg.dynamicSmemBytes = jacobi_cluster_smem_bytes(k);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = kJcCtas;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const float *core = ws->core;
+        float *vc = ws->vc, *uc = ws->uc;
+        err = k <= 128 ? cudaLaunchKernelEx(&cfg, jacobi_svd_cluster_kernel<128>, core, k, d_S, vc, uc)
+                       : cudaLaunchKernelEx(&cfg, jacobi_svd_cluster_kernel<256>, core, k, d_S, vc, uc);
+        if (err != cudaSuccess) return err;
+    } else if (ws->own_core_svd) {
         jacobi_svd_kernel<<<1, 512, jacobi_smem_bytes(k), st>>>(ws->core, k, d_S, ws->vc, ws->uc);
         if ((err = cudaGetLastError()) != cudaSuccess) return err;
     } else if (cusolverDnSgesvdj(ws->solver, CUSOLVER_EIG_MODE_VECTOR, 0, k, k, ws->core, k, d_S, ws->vc, k, ws->uc, k,
