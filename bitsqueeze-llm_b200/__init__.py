@@ -100,6 +100,7 @@ CXX_SYMBOLS = [
     "_Z26bitsqz_llm_get_packed_sizePK16bitsqz_llm_array",
     "_Z27load_bitsqz_llm_from_bufferPKvm",
     "_Z15bitsqz_llm_freeP16bitsqz_llm_array",
+    "_Z29topk_compute_num_topk_columnstf",
 ]
 
 _lib = None

@@ -829,3 +829,10 @@ void bitsqz_llm_free(bitsqz_llm_array_t *compressed) {
     if (!compressed) return;
     if (!host_pool().give_back(compressed)) std::free(compressed);
 }
+
+// The reference's integration tests and walkthrough also call this helper of its top-k module
+// (modules/topk_cuda/include/topk_cuda.cuh:47, topk_cuda.cu:53-69); exported under the same C++ name so that they
+// link against this library unchanged.
+uint16_t topk_compute_num_topk_columns(uint16_t num_columns, float topk_ratio) {
+    return (uint16_t)bsq::topk_num_columns(num_columns, topk_ratio);
+}

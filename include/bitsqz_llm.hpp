@@ -155,6 +155,12 @@ BITSQZ_LLM_API bitsqz_llm_array_t *load_bitsqz_llm_from_buffer(const void *buffe
 // Reference: :141, src/bitsqz_llm.cu:1452-1455.
 BITSQZ_LLM_API void bitsqz_llm_free(bitsqz_llm_array_t *compressed);
 
+// Not part of the reference's bitsqz_llm.hpp: the column-count helper of its top-k module
+// (modules/topk_cuda/include/topk_cuda.cuh:47), which its own integration tests and walkthrough call next to the
+// functions above; exported under the same C++ name.  k = (uint16_t)roundf(num_columns * topk_ratio), at most
+// num_columns, at least 1 for a positive ratio.
+BITSQZ_LLM_API uint16_t topk_compute_num_topk_columns(uint16_t num_columns, float topk_ratio);
+
 static_assert(sizeof(bitsqz_section_t) == 24, "section entry is 24 bytes");
 static_assert(sizeof(bitsqz_llm_array_t) == 200, "array header is 200 bytes");
 static_assert(offsetof(bitsqz_llm_array_t, flags) == 40, "flags at byte 40");
