@@ -57,7 +57,7 @@ struct SvdWorkspace {
     unsigned *status = nullptr;         // device status word of the current call
     unsigned *own_status = nullptr;     // used when the caller passes none
     bool own_core_svd = false;          // k small enough for jacobi_svd_kernel (else cuSOLVER's gesvdj on the core)
-    bool seeded = false;                // the generator holds `seed` (seeding costs a kernel of its own)
+    bool seeded = false;                // omega holds the draw for `seed`
     unsigned long long seed = 0;
 };
 
@@ -227,7 +227,8 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_smem_kernel(const float
 //   factorisation, per block column J: warp 0 factors the diagonal block in registers (one column per lane, the
 //       pivot row travels by shuffles); every thread then solves one column of the block row against it
 //       (R_JJ^T Y = G_JC, forward substitution), and all threads apply the rank-32 update to the trailing blocks;
-//       every sum runs in the order of the unblocked algorithm, so R comes out bit-identical to it;
+//       every sum runs in the order of the unblocked algorithm (the pivots use a reciprocal square root, so R agrees
+//       with it to rounding, not bit for bit);
 //   inverse: the diagonal blocks are inverted by one warp each, all at once; block column J of T = R^-1 is then
 //       T_IJ = -(sum_{L=I..J-1} T_IL R_LJ) T_JJ, two rounds of 32 x 32 block products per column.
 constexpr int kCholeskyBlockedMaxK = 256;
@@ -240,6 +241,29 @@ __host__ __device__ constexpr size_t cholesky_blocked_smem_bytes(int k) {
 }
 __device__ __forceinline__ int blk_id(int I, int J, int nb) { return I * nb - (I * (I - 1)) / 2 + (J - I); }
 
+// Four 32 x 32 block products at a time: a quarter of the CTA (256 threads) per product, 2 x 2 outputs per thread
+// (rows 2 ti, 2 ti + 1, columns 2 tc, 2 tc + 1), operands read as float2.
+//   out -= A^T B  (AT = true:  A, B hold the contraction index in rows)
+//   out += A B    (AT = false: A holds it in columns)
+template <bool AT>
+__device__ __forceinline__ void block_mac(float (&acc)[2][2], const float *__restrict__ A, const float *__restrict__ B, int ti, int tc) {
+#pragma unroll 8
+    for (int l = 0; l < kCB; ++l) {
+        const float2 b = *reinterpret_cast<const float2 *>(B + l * kCB + 2 * tc);
+        float a0, a1;
+        if (AT) {
+            const float2 a = *reinterpret_cast<const float2 *>(A + l * kCB + 2 * ti);
+            a0 = -a.x;
+            a1 = -a.y;
+        } else {
+            a0 = A[(2 * ti) * kCB + l];
+            a1 = A[(2 * ti + 1) * kCB + l];
+        }
+        acc[0][0] += a0 * b.x; acc[0][1] += a0 * b.y;
+        acc[1][0] += a1 * b.x; acc[1][1] += a1 * b.y;
+    }
+}
+
 __global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const float *__restrict__ G, int k, float *__restrict__ T,
                                                                         float *__restrict__ Rcpy) {
     extern __shared__ float sm[];
@@ -250,35 +274,29 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const fl
     float *dinv = tmp + (size_t)nb * kCB * kCB;            // 1 / R(i, i)
     float *red = dinv + nb * kCB;                          // 32 + 1
     const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
-    // load, padded with an identity; the part of a diagonal block below the diagonal is never read.
-    // Four elements per thread and trip, so that four global loads are in flight at a time.
+    const int bi = tid >> 5, bc = tid & 31;               // this thread's element of a block when the CTA walks blocks
+    const int quarter = tid >> 8, ti = (tid & 255) >> 4, tc = tid & 15;   // ... and its 2 x 2 tile of a quarter's block
+    // load block by block (row bi, column bc of each), padded with an identity; what lies below the diagonal of a
+    // diagonal block is never read.  Four blocks per trip, so that four global loads are in flight per thread.
     float md = 0.0f;
-    for (int e0 = tid; e0 < nbt * kCB * kCB; e0 += 4 * nt) {
+    for (int b0 = 0; b0 < nbt; b0 += 4) {
         float v[4];
-        int pos[4];
-        bool diag[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const int e = e0 + u * nt;
-            pos[u] = -1;
-            diag[u] = false;
+            const int b = b0 + u;
             v[u] = 0.0f;
-            if (e < nbt * kCB * kCB) {
-                const int b = e / (kCB * kCB), w = e % (kCB * kCB);
+            if (b < nbt) {
                 int I = 0, rem = b;
                 while (rem >= nb - I) { rem -= nb - I; ++I; }      // block (I, I + rem)
-                const int i = I * kCB + w / kCB, c = (I + rem) * kCB + w % kCB;
-                pos[u] = e;
-                diag[u] = i == c && i < k;
+                const int i = I * kCB + bi, c = (I + rem) * kCB + bc;
                 v[u] = (i == c) ? 1.0f : 0.0f;
                 if (i < k && c < k) v[u] = G[(size_t)i * k + c];
+                if (i == c && i < k) md = fmaxf(md, v[u]);
             }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            if (pos[u] >= 0) blocks[pos[u]] = v[u];
-            if (diag[u]) md = fmaxf(md, v[u]);
-        }
+        for (int u = 0; u < 4; ++u)
+            if (b0 + u < nbt) blocks[(size_t)(b0 + u) * kCB * kCB + tid] = v[u];
     }
     for (int d = 16; d > 0; d >>= 1) md = fmaxf(md, __shfl_xor_sync(0xffffffffu, md, d));
     if (lane == 0) red[warp] = md;
@@ -304,8 +322,15 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const fl
             for (int j = 0; j < kCB; ++j) {
                 float d = __shfl_sync(0xffffffffu, a[j], j);
                 if (!(d > 0.5f * shift)) d = 0.5f * shift;
-                const float r = d > 0.0f ? sqrtf(d) : 0.0f;
-                const float inv = r > 0.0f ? 1.0f / r : 0.0f;
+                // the 32 pivots of a block are one dependent chain: reciprocal square root from the special-function
+                // unit plus one Newton step (a relative error of ~1e-7 in R(j, j) and 1 / R(j, j) alike) instead of
+                // an IEEE square root followed by an IEEE division
+                float inv = 0.0f;
+                if (d > 0.0f) {
+                    inv = rsqrtf(d);
+                    inv = inv * (1.5f - 0.5f * d * inv * inv);
+                }
+                const float r = d * inv;
                 a[j] = (lane == j) ? r : a[j] * inv;
                 if (lane == j) my_inv = inv;
 #pragma unroll
@@ -334,30 +359,43 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const fl
             for (int i = 0; i < kCB; ++i) X[i * kCB] = y[i];
         }
         __syncthreads();
-        // trailing blocks (A, B), J < A <= B: G_AB -= R_JA^T R_JB, one 32 x 32 block per pass
+        // trailing blocks (A, B), J < A <= B: G_AB -= R_JA^T R_JB, four blocks per trip
         {
             const int rest = nb - J - 1, pairs = rest * (rest + 1) / 2;
-            const int i = tid / kCB, c = tid % kCB;
-            for (int pr = 0; pr < pairs; ++pr) {
-                int A = 0, rem = pr;
-                while (rem >= rest - A) { rem -= rest - A; ++A; }
-                const int B = A + rem;
-                const float *RA = blocks + (size_t)blk_id(J, J + 1 + A, nb) * kCB * kCB;
-                const float *RB = blocks + (size_t)blk_id(J, J + 1 + B, nb) * kCB * kCB;
-                float *O = blocks + (size_t)blk_id(J + 1 + A, J + 1 + B, nb) * kCB * kCB;
-                float acc = O[i * kCB + c];
-#pragma unroll
-                for (int l = 0; l < kCB; ++l) acc -= RA[l * kCB + i] * RB[l * kCB + c];
-                O[i * kCB + c] = acc;
+            for (int pr0 = 0; pr0 < pairs; pr0 += 4) {
+                const int pr = pr0 + quarter;
+                if (pr < pairs) {
+                    int A = 0, rem = pr;
+                    while (rem >= rest - A) { rem -= rest - A; ++A; }
+                    const int B = A + rem;
+                    const float *RA = blocks + (size_t)blk_id(J, J + 1 + A, nb) * kCB * kCB;
+                    const float *RB = blocks + (size_t)blk_id(J, J + 1 + B, nb) * kCB * kCB;
+                    float *O = blocks + (size_t)blk_id(J + 1 + A, J + 1 + B, nb) * kCB * kCB;
+                    float2 *o0 = reinterpret_cast<float2 *>(O + (2 * ti) * kCB + 2 * tc);
+                    float2 *o1 = reinterpret_cast<float2 *>(O + (2 * ti + 1) * kCB + 2 * tc);
+                    float acc[2][2] = {{o0->x, o0->y}, {o1->x, o1->y}};
+                    block_mac<true>(acc, RA, RB, ti, tc);
+                    *o0 = make_float2(acc[0][0], acc[0][1]);
+                    *o1 = make_float2(acc[1][0], acc[1][1]);
+                }
             }
         }
         __syncthreads();
     }
-    // R out; zeros of T below the diagonal; the diagonal blocks' inverses, one warp each
-    for (int e = tid; e < k * k; e += nt) {
-        const int i = e / k, c = e % k;
-        if (Rcpy) Rcpy[e] = c < i ? 0.0f : blocks[(size_t)blk_id(i / kCB, c / kCB, nb) * kCB * kCB + (i % kCB) * kCB + c % kCB];
-        if (c < i) T[e] = 0.0f;
+    // R out and the zeros below the diagonal of R and T, block by block; the diagonal blocks' inverses, one warp each
+    for (int I = 0; I < nb; ++I) {
+        for (int Jb = 0; Jb < nb; ++Jb) {
+            const int i = I * kCB + bi, c = Jb * kCB + bc;
+            if (i < k && c < k) {
+                const size_t e = (size_t)i * k + c;
+                if (c < i) {
+                    T[e] = 0.0f;
+                    if (Rcpy) Rcpy[e] = 0.0f;
+                } else if (Rcpy) {
+                    Rcpy[e] = blocks[(size_t)blk_id(I, Jb, nb) * kCB * kCB + tid];
+                }
+            }
+        }
     }
     if (warp < nb) {
         const float *D = blocks + (size_t)blk_id(warp, warp, nb) * kCB * kCB;
@@ -378,36 +416,41 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const fl
     }
     __syncthreads();
     // block column J of T, from the left: needs T_IL for L < J (already in place) and R_LJ (still in place)
-    {
-        const int i = tid / kCB, c = tid % kCB;
-        for (int J = 1; J < nb; ++J) {
-            for (int I = 0; I < J; ++I) {
-                float acc = 0.0f;
+    for (int J = 1; J < nb; ++J) {
+        for (int I0 = 0; I0 < J; I0 += 4) {
+            const int I = I0 + quarter;
+            if (I < J) {
+                float acc[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
                 for (int L = I; L < J; ++L) {
                     const float *TL = (L == I) ? tinv + (size_t)I * kCB * kCB : blocks + (size_t)blk_id(I, L, nb) * kCB * kCB;
-                    const float *RL = blocks + (size_t)blk_id(L, J, nb) * kCB * kCB;
-#pragma unroll
-                    for (int l = 0; l < kCB; ++l) acc += TL[i * kCB + l] * RL[l * kCB + c];
+                    block_mac<false>(acc, TL, blocks + (size_t)blk_id(L, J, nb) * kCB * kCB, ti, tc);
                 }
-                tmp[(size_t)I * kCB * kCB + i * kCB + c] = acc;
+                float *O = tmp + (size_t)I * kCB * kCB;
+                *reinterpret_cast<float2 *>(O + (2 * ti) * kCB + 2 * tc) = make_float2(acc[0][0], acc[0][1]);
+                *reinterpret_cast<float2 *>(O + (2 * ti + 1) * kCB + 2 * tc) = make_float2(acc[1][0], acc[1][1]);
             }
-            __syncthreads();
-            const float *TJ = tinv + (size_t)J * kCB * kCB;
-            for (int I = 0; I < J; ++I) {
-                float acc = 0.0f;
-#pragma unroll
-                for (int l = 0; l < kCB; ++l) acc -= tmp[(size_t)I * kCB * kCB + i * kCB + l] * TJ[l * kCB + c];
-                blocks[(size_t)blk_id(I, J, nb) * kCB * kCB + i * kCB + c] = acc;
-            }
-            __syncthreads();
         }
+        __syncthreads();
+        const float *TJ = tinv + (size_t)J * kCB * kCB;
+        for (int I0 = 0; I0 < J; I0 += 4) {
+            const int I = I0 + quarter;
+            if (I < J) {
+                float acc[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
+                block_mac<false>(acc, tmp + (size_t)I * kCB * kCB, TJ, ti, tc);
+                float *O = blocks + (size_t)blk_id(I, J, nb) * kCB * kCB;
+                *reinterpret_cast<float2 *>(O + (2 * ti) * kCB + 2 * tc) = make_float2(-acc[0][0], -acc[0][1]);
+                *reinterpret_cast<float2 *>(O + (2 * ti + 1) * kCB + 2 * tc) = make_float2(-acc[1][0], -acc[1][1]);
+            }
+        }
+        __syncthreads();
     }
-    for (int e = tid; e < k * k; e += nt) {
-        const int i = e / k, c = e % k;
-        if (c >= i) {
-            const int I = i / kCB, Jb = c / kCB;
-            const float *src = (I == Jb) ? tinv + (size_t)I * kCB * kCB : blocks + (size_t)blk_id(I, Jb, nb) * kCB * kCB;
-            T[e] = src[(i % kCB) * kCB + c % kCB];
+    for (int I = 0; I < nb; ++I) {
+        for (int Jb = I; Jb < nb; ++Jb) {
+            const int i = I * kCB + bi, c = Jb * kCB + bc;
+            if (i < k && c < k && c >= i) {
+                const float *src = (I == Jb) ? tinv + (size_t)I * kCB * kCB : blocks + (size_t)blk_id(I, Jb, nb) * kCB * kCB;
+                T[(size_t)i * k + c] = src[tid];
+            }
         }
     }
 }
@@ -893,16 +936,17 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
     if (!d_status && cudaMemsetAsync(ws->own_status, 0, sizeof(unsigned), st) != cudaSuccess) return cudaErrorUnknown;
     if (curandSetStream(ws->rng, st) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
     if (cusolverDnSetStream(ws->solver, st) != CUSOLVER_STATUS_SUCCESS) return cudaErrorUnknown;
+    // Omega depends on the seed and the shape only (the generator is set back to the start of the seed's sequence for
+    // every call), so it is drawn once per workspace and seed and kept: re-seeding costs a kernel of its own.
     if (!ws->seeded || ws->seed != seed) {
         if (curandSetPseudoRandomGeneratorSeed(ws->rng, seed) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
+        if (curandSetGeneratorOffset(ws->rng, 0ULL) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
+        size_t count = (size_t)ws->N * k;
+        count += count & 1;                               // the normal generator wants an even count
+        if (curandGenerateNormal(ws->rng, ws->omega, count, 0.0f, 1.0f) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
         ws->seeded = true;
         ws->seed = seed;
     }
-    // back to the start of the seed's sequence: every call draws the same Omega
-    if (curandSetGeneratorOffset(ws->rng, 0ULL) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
-    size_t count = (size_t)ws->N * k;
-    count += count & 1;                                   // the normal generator wants an even count
-    if (curandGenerateNormal(ws->rng, ws->omega, count, 0.0f, 1.0f) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
 
     cudaError_t err;
     float *q = nullptr, *qz = nullptr, *spare = nullptr;
