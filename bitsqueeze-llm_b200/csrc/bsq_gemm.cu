@@ -169,8 +169,17 @@ __global__ void reduce_splits_kernel(const float *__restrict__ part, float *__re
     const long total = (long)M * N;
     for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) {
         const int i = (int)(e / N), j = (int)(e % N);
+        // eight loads in flight, added in split order (the order fixes the result bit for bit)
         float s = 0.0f;
-        for (int z = 0; z < splits; ++z) s += part[z * split_stride + (long)i * N + j];
+        int z = 0;
+        for (; z + 8 <= splits; z += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = part[(z + u) * split_stride + (long)i * N + j];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) s += v[u];
+        }
+        for (; z < splits; ++z) s += part[z * split_stride + (long)i * N + j];
         C[(long)i * ldc + j] = s;
     }
 }
