@@ -53,6 +53,8 @@ CASES = [
     (100, 200, 0.03, 0.02, 10, 1),          # blocks straddle rows, generic top-k
     (64, 1000, 0.01, 0.0, 11, 1),
     (33, 4096, 0.005, 0.01, 11, 1),
+    (192, 14336, 0.005, 0.0, 10, 1),        # row length of BASELINE configs[4] (k = 72): 8 warps per row
+    (192, 14336, 0.005, 0.01, 11, 1),       # ... with error correction (k = 143)
     (128, 512, 0.0, 0.0, -1, 1),            # dense FP32 section
     (128, 512, 0.02, 0.0, -1, 0),
 ]
