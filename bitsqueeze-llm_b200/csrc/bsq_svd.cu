@@ -20,6 +20,7 @@
 // everything that touches an M- or N-sized array, is a kernel of this library.
 // Omega comes from cuRAND's XORWOW generator like the reference's (svd_lowrank_cuda.cu:143,289-291),
 // seeded per call, column-major N x k.
+#include "bsq_device.cuh"
 #include "bsq_internal.hpp"
 
 #include <cooperative_groups.h>
@@ -56,6 +57,7 @@ struct SvdWorkspace {
     void *allreduce_ctx = nullptr;
     unsigned *status = nullptr;         // device status word of the current call
     unsigned *own_status = nullptr;     // used when the caller passes none
+    int jc_lanes = 4;                   // lanes per column pair of the cluster Jacobi kernel for this k
     bool own_core_svd = false;          // k small enough for jacobi_svd_kernel (else cuSOLVER's gesvdj on the core)
     bool seeded = false;                // omega holds the draw for `seed`
     unsigned long long seed = 0;
@@ -607,36 +609,69 @@ __global__ void __launch_bounds__(512) jacobi_svd_kernel(const float *__restrict
 // identical angles.  Control flow is the same in all CTAs by construction (same data, same arithmetic), which is
 // what the hardware cluster barrier needs; the sweep count is bounded.
 constexpr int kJacobiClusterMaxK = 256;
-constexpr int kJcCtas = 8;                                   // 16 measured slower: the barrier and the remote stores grow
+constexpr int kJcCtas = 8;                                   // 16 measured slower: the partial products take longer to arrive
 __host__ __device__ constexpr int jacobi_cluster_len(int k) { return k <= 128 ? 128 : 256; }     // padded column length
 __host__ __device__ constexpr size_t jacobi_cluster_smem_bytes(int k) {
-    // M and V slices, norms, two rounds of kJcCtas x LEN / 2 partial products, kJcCtas x LEN partial norms, ranks
+    // M and V slices, norms, two rounds of CTAs x LEN / 2 partial products, CTAs x LEN partial norms, ranks, votes, mbarriers
     return ((size_t)2 * ((k + 1) & ~1) * (jacobi_cluster_len(k) / kJcCtas) + ((k + 1) & ~1) + kJcCtas * jacobi_cluster_len(k) +
-            kJcCtas * jacobi_cluster_len(k) + jacobi_cluster_len(k) + 64) * sizeof(float);
+            kJcCtas * jacobi_cluster_len(k) + jacobi_cluster_len(k) + 64) *
+           sizeof(float);
 }
 
-template <int kJcLen>
-__global__ void __launch_bounds__(2 * kJcLen) jacobi_svd_cluster_kernel(const float *__restrict__ C, int k, float *__restrict__ S,
-                                                                        float *__restrict__ Ucol, float *__restrict__ Vcol) {
-    constexpr int kJcRows = kJcLen / kJcCtas, kJcF4 = kJcRows / 16;      // rows per CTA; float4 per lane and column
+// The shared::cluster address of `smem_addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster.
+__device__ __forceinline__ unsigned cluster_addr(unsigned smem_addr, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+// 16-byte store into another CTA's shared memory that counts itself off on that CTA's mbarrier when it has landed:
+// the receiver waits for the bytes, no fence and no cluster-wide barrier on the sender's side.
+__device__ __forceinline__ void st_async_f4(unsigned dst, const float4 &v, unsigned mbar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(dst), "f"(v.x),
+                 "f"(v.y), "f"(v.z), "f"(v.w), "r"(mbar)
+                 : "memory");
+}
+
+template <int kJcLen, int kLpp>
+__global__ void __launch_bounds__(kJcLen / 2 * kLpp, 1) jacobi_svd_cluster_kernel(const float *__restrict__ C, int k, float *__restrict__ S,
+                                                                        float *__restrict__ Ucol, float *__restrict__ Vcol,
+                                                                        unsigned *__restrict__ status) {
+    constexpr int kJcRows = kJcLen / kJcCtas, kJcF4 = kJcRows / (4 * kLpp);      // rows per CTA; float4 per lane and column
+    static_assert(kLpp == 2 || kLpp == 4, "lanes per column pair");
+    static_assert(kJcF4 == 1 || kJcF4 == 2 || kJcF4 == 4, "float4 per lane and column");
+    constexpr int kSlots = kJcLen / 2;                                   // pair slots = partial products per CTA and round
+    constexpr unsigned kRoundBytes = kJcCtas * kSlots * sizeof(float);   // what one CTA receives per round
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned cr = cluster.block_rank();                 // this CTA holds rows cr * kJcRows .. + kJcRows - 1
     extern __shared__ __align__(16) float sm[];
     const int kp = (k + 1) & ~1, npairs = kp / 2;
     float *M = sm, *V = M + (size_t)kp * kJcRows, *nrm = V + (size_t)kp * kJcRows;
-    float *part = nrm + kp;                                   // [2][4][128]
-    float *npart = part + 2 * kJcCtas * (kJcLen / 2);         // [4][256]
+    float *part = nrm + ((kp + 3) & ~3);                      // [2][kJcCtas][kSlots], 16-byte aligned
+    float *npart = part + 2 * kJcCtas * kSlots;               // [kJcCtas][kJcLen]
     int *rank_of = reinterpret_cast<int *>(npart + kJcCtas * kJcLen);
-    float *part_at[kJcCtas], *npart_at[kJcCtas];              // the same arrays in every CTA of the cluster
-#pragma unroll
-    for (int d = 0; d < kJcCtas; ++d) {
-        part_at[d] = cluster.map_shared_rank(part, d);
-        npart_at[d] = cluster.map_shared_rank(npart, d);
-    }
-    const int tid = threadIdx.x, nt = blockDim.x;
-    const int slot = tid >> 2, l = tid & 3;                   // 4 lanes per pair, 128 pair slots, kJcF4 float4 per lane and column
+    int *votes = rank_of + kJcLen;                            // [kJcCtas]
+    uint64_t *mbar = reinterpret_cast<uint64_t *>(votes + kJcCtas);      // [2], one per parity of the round counter
+    const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31;
+    const int slot = tid / kLpp, l = tid % kLpp;              // kLpp lanes per pair, kSlots pair slots, kJcF4 float4 per lane and column
+    // A warp holds 32 / kLpp pair slots, that many partial products per round, in groups of four: the warp is cut
+    // into as many parts as it has groups, and in each part lane d (d < 8) sends the part's group as one 16-byte
+    // store to CTA d.
+    static_assert(kJcCtas == 8, "one sending lane per destination CTA and group");
+    constexpr int kPartLanes = 4 * kLpp;                      // lanes that own one group of four slots
+    const int part_lane0 = lane / kPartLanes * kPartLanes;
+    const bool sender = lane - part_lane0 < kJcCtas;
+    const unsigned part_to = cluster_addr(smem_u32(part + cr * kSlots + (tid >> 5) * (32 / kLpp) + part_lane0 / kLpp), lane & 7);
+    const unsigned mbar_to = cluster_addr(smem_u32(mbar), lane & 7);
+    // A column slice of more than one float4 per lane starts at a multiple of 128 bytes, the same banks for every
+    // slot: slot s takes its float4 in the order f ^ (s mod kJcF4), so neighbouring slots spread over all banks.
+    const int fsw = slot & (kJcF4 - 1);
     const int row0 = cr * kJcRows;
+    if (tid == 0) {
+        mbar_init(&mbar[0], 1);
+        mbar_init(&mbar[1], 1);
+        mbar_fence_init();
+    }
     for (int e0 = tid; e0 < kp * kJcRows; e0 += 4 * nt) {
         float v[4];
 #pragma unroll
@@ -655,83 +690,130 @@ __global__ void __launch_bounds__(2 * kJcLen) jacobi_svd_cluster_kernel(const fl
     }
     __syncthreads();
     const float tol = sqrtf((float)kJcLen) * 5.9604645e-08f, tol2 = tol * tol;
-    auto sum4 = [&](float x) {
-        x += __shfl_xor_sync(0xffffffffu, x, 2, 4);
-        x += __shfl_xor_sync(0xffffffffu, x, 1, 4);
+    auto sum4 = [&](float x) {                                // over the lanes of a pair
+        if (kLpp == 4) x += __shfl_xor_sync(0xffffffffu, x, 2, 4);
+        x += __shfl_xor_sync(0xffffffffu, x, 1, kLpp);
         return x;
     };
-    // exact squared norms of all columns: partial over this CTA's rows, exchanged, added in CTA order
-    auto exact_norms = [&](bool root) {
-        for (int j0 = 0; j0 < kp; j0 += nt / 4) {             // uniform trip count: shuffles inside
+    // Exact squared norms of all columns (partial over this CTA's rows, exchanged, added in CTA order) and, on the
+    // same cluster barrier, the CTAs' votes: bit 0 = "rotated a pair in the last sweep", bit 1 = "a wait ran out".
+    // Every CTA reads the same eight votes, so all of them leave the sweep loop in the same sweep whatever happened.
+    // (The first of these barriers also makes the mbarriers' initialisation known to the whole cluster.)
+    auto norms_and_votes = [&](int my_vote) {
+        for (int j0 = 0; j0 < kp; j0 += nt / kLpp) {          // uniform trip count: shuffles inside
             const int j = j0 + slot;
             float acc = 0.0f;
             if (j < kp) {
 #pragma unroll
                 for (int f = 0; f < kJcF4; ++f) {
-                    const float4 a = reinterpret_cast<const float4 *>(M + (size_t)j * kJcRows)[f * 4 + l];
+                    const float4 a = reinterpret_cast<const float4 *>(M + (size_t)j * kJcRows)[f * kLpp + l];
                     acc += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
                 }
             }
             acc = sum4(acc);
             if (l == 0 && j < kp) {
 #pragma unroll
-                for (int d = 0; d < kJcCtas; ++d) npart_at[d][cr * kJcLen + j] = acc;
+                for (int d = 0; d < kJcCtas; ++d) cluster.map_shared_rank(npart, d)[cr * kJcLen + j] = acc;
             }
         }
+        if (tid < kJcCtas) cluster.map_shared_rank(votes, tid)[cr] = my_vote;
         cluster.sync();
         for (int j = tid; j < kp; j += nt) {
             float a = 0.0f;
 #pragma unroll
             for (int d = 0; d < kJcCtas; ++d) a += npart[d * kJcLen + j];
-            nrm[j] = root ? sqrtf(a) : a;
+            nrm[j] = a;
         }
+        int all = 0;
+#pragma unroll
+        for (int d = 0; d < kJcCtas; ++d) all |= votes[d];
         __syncthreads();
+        return all;
     };
-    for (int sweep = 0; sweep < kJacobiMaxSweeps; ++sweep) {
-        exact_norms(false);
+    // The rotation of V's columns is not needed before the next round's end (nothing reads V to take a decision),
+    // so it is kept back and done while the next round's partial products are in flight.
+    // Columns p, q of one round belong to one pair slot; the barrier at the end of every round orders this slot's
+    // late rotation before the rotation that the columns' next owners keep back in their turn.
+    int dv_p = 0, dv_q = 0;
+    float dv_c = 1.0f, dv_sn = 0.0f;
+    bool dv_pending = false;
+    auto apply_to_v = [&]() {
+        if (!dv_pending) return;
+        float4 *vp = reinterpret_cast<float4 *>(V + (size_t)dv_p * kJcRows), *vq = reinterpret_cast<float4 *>(V + (size_t)dv_q * kJcRows);
+        const float c = dv_c, sn = dv_sn;
+#pragma unroll
+        for (int f = 0; f < kJcF4; ++f) {
+            const int i4 = (f ^ fsw) * kLpp + l;
+            const float4 u = vp[i4], w = vq[i4];
+            vp[i4] = make_float4(c * u.x - sn * w.x, c * u.y - sn * w.y, c * u.z - sn * w.z, c * u.w - sn * w.w);
+            vq[i4] = make_float4(sn * u.x + c * w.x, sn * u.y + c * w.y, sn * u.z + c * w.z, sn * u.w + c * w.w);
+        }
+        dv_pending = false;
+    };
+    // One round's exchange: every CTA sends its kSlots partial products to all eight (itself included) with stores
+    // that count off on the receiver's mbarrier of the round's parity; a receiver's phase ends when all
+    // kRoundBytes are there.  Two buffers and two mbarriers are enough: a CTA sends round i + 2 only after it has
+    // round i + 1 from everybody, and everybody sent round i + 1 after the CTA barrier that ends its round i, so
+    // nobody still reads or waits for round i then.
+    int vote = 1;
+    bool failed = false;                                      // a wait ran out: stop sending and waiting, finish quickly
+    unsigned it = 0;                                          // rounds so far
+    for (int sweep = 0;; ++sweep) {
+        const int all = norms_and_votes(vote);
+        if (!(all & 1) || (all & 2) || sweep == kJacobiMaxSweeps) break;
         bool rotated = false;
-        for (int r = 0; r < kp - 1; ++r) {
+        for (int r = 0; r < kp - 1; ++r, ++it) {
+            const unsigned par = it & 1, phase = (it >> 1) & 1;
+            if (tid == 0) mbar_expect_tx(&mbar[par], kRoundBytes);
             const bool active = slot < npairs;
             int p = 0, q = 0;
             if (active) {
                 if (slot == 0) { p = kp - 1; q = r; }
-                else { p = (r + slot) % (kp - 1); q = (r + kp - 1 - slot) % (kp - 1); }
+                else {                                        // (r + slot) mod (kp - 1) and (r - slot) mod (kp - 1)
+                    p = r + slot;
+                    q = r + kp - 1 - slot;
+                    p -= p >= kp - 1 ? kp - 1 : 0;
+                    q -= q >= kp - 1 ? kp - 1 : 0;
+                }
             }
             float4 *mp = reinterpret_cast<float4 *>(M + (size_t)p * kJcRows), *mq = reinterpret_cast<float4 *>(M + (size_t)q * kJcRows);
             float4 ap[kJcF4], aq[kJcF4];
             float g = 0.0f;
 #pragma unroll
             for (int f = 0; f < kJcF4; ++f) {
-                ap[f] = mp[f * 4 + l];
-                aq[f] = mq[f * 4 + l];
+                ap[f] = mp[(f ^ fsw) * kLpp + l];
+                aq[f] = mq[(f ^ fsw) * kLpp + l];
                 g += ap[f].x * aq[f].x + ap[f].y * aq[f].y + ap[f].z * aq[f].z + ap[f].w * aq[f].w;
             }
-            g = sum4(g);
-            const int par = r & 1;
-            if (l == 0) {
-#pragma unroll
-                for (int d = 0; d < kJcCtas; ++d) part_at[d][(par * kJcCtas + cr) * (kJcLen / 2) + slot] = g;
-            }
-            cluster.sync();                                   // partials of this round are everywhere
-            const float *pp = part + par * kJcCtas * (kJcLen / 2) + slot;
-            g = 0.0f;
-#pragma unroll
-            for (int d = 0; d < kJcCtas; ++d) g += pp[d * (kJcLen / 2)];
             const float alpha = nrm[p], beta = nrm[q];
+            g = sum4(g);
+            {
+                float4 g4;
+                g4.x = __shfl_sync(0xffffffffu, g, part_lane0);
+                g4.y = __shfl_sync(0xffffffffu, g, part_lane0 + kLpp);
+                g4.z = __shfl_sync(0xffffffffu, g, part_lane0 + 2 * kLpp);
+                g4.w = __shfl_sync(0xffffffffu, g, part_lane0 + 3 * kLpp);
+                if (sender && !failed)
+                    st_async_f4(part_to + par * (unsigned)(kJcCtas * kSlots * sizeof(float)), g4, mbar_to + par * (unsigned)sizeof(uint64_t));
+            }
+            apply_to_v();                                     // the previous round's rotation of V, while the stores travel
+            if (!failed) failed = !mbar_wait_bounded(&mbar[par], phase, status);
+            const float *pp = part + par * kJcCtas * kSlots + slot;
+            g = ((pp[0] + pp[kSlots]) + (pp[2 * kSlots] + pp[3 * kSlots])) + ((pp[4 * kSlots] + pp[5 * kSlots]) + (pp[6 * kSlots] + pp[7 * kSlots]));
             if (active && alpha > 0.0f && beta > 0.0f && g * g > tol2 * alpha * beta) {
-                const float zeta = (beta - alpha) / (2.0f * g);
-                const float t = fabsf(zeta) > 1.0e8f ? 0.5f / zeta : copysignf(1.0f, zeta) / (fabsf(zeta) + sqrtf(1.0f + zeta * zeta));
-                const float c = rsqrtf(1.0f + t * t), sn = c * t;
-                float4 *vp = reinterpret_cast<float4 *>(V + (size_t)p * kJcRows), *vq = reinterpret_cast<float4 *>(V + (size_t)q * kJcRows);
+                // tangent, cosine and sine to a few units in the last place: what they leave of the pair's
+                // product is far below the tolerance, and every CTA gets the same bits from the same inputs
+                const float zeta = __fdividef(beta - alpha, 2.0f * g);
+                const float w = fmaf(zeta, zeta, 1.0f);
+                const float t = fabsf(zeta) > 1.0e8f ? __fdividef(0.5f, zeta) : __fdividef(copysignf(1.0f, zeta), fabsf(zeta) + w * rsqrtf(w));
+                const float c = rsqrtf(fmaf(t, t, 1.0f)), sn = c * t;
 #pragma unroll
                 for (int f = 0; f < kJcF4; ++f) {
                     const float4 x = ap[f], y = aq[f];
-                    mp[f * 4 + l] = make_float4(c * x.x - sn * y.x, c * x.y - sn * y.y, c * x.z - sn * y.z, c * x.w - sn * y.w);
-                    mq[f * 4 + l] = make_float4(sn * x.x + c * y.x, sn * x.y + c * y.y, sn * x.z + c * y.z, sn * x.w + c * y.w);
-                    const float4 u = vp[f * 4 + l], w = vq[f * 4 + l];
-                    vp[f * 4 + l] = make_float4(c * u.x - sn * w.x, c * u.y - sn * w.y, c * u.z - sn * w.z, c * u.w - sn * w.w);
-                    vq[f * 4 + l] = make_float4(sn * u.x + c * w.x, sn * u.y + c * w.y, sn * u.z + c * w.z, sn * u.w + c * w.w);
+                    mp[(f ^ fsw) * kLpp + l] = make_float4(c * x.x - sn * y.x, c * x.y - sn * y.y, c * x.z - sn * y.z, c * x.w - sn * y.w);
+                    mq[(f ^ fsw) * kLpp + l] = make_float4(sn * x.x + c * y.x, sn * x.y + c * y.y, sn * x.z + c * y.z, sn * x.w + c * y.w);
                 }
+                dv_p = p; dv_q = q; dv_c = c; dv_sn = sn; dv_pending = true;
                 if (l == 0) {
                     nrm[p] = fmaxf(alpha - t * g, 0.0f);
                     nrm[q] = beta + t * g;
@@ -740,9 +822,11 @@ __global__ void __launch_bounds__(2 * kJcLen) jacobi_svd_cluster_kernel(const fl
             }
             __syncthreads();                                  // this CTA's slices are rotated before the next round reads them
         }
-        if (!__syncthreads_or(rotated)) break;               // the same answer in every CTA: they rotated with the same numbers
+        vote = (__syncthreads_or(rotated) ? 1 : 0) | (__syncthreads_or(failed) ? 2 : 0);
     }
-    exact_norms(true);                                        // nrm = singular values
+    apply_to_v();                                             // the last rotation kept back
+    for (int j = tid; j < kp; j += nt) nrm[j] = sqrtf(nrm[j]);           // singular values: the norms are fresh, nothing rotated since
+    __syncthreads();
     for (int j = tid; j < k; j += nt) {
         const float sj = nrm[j];
         int rk = 0;
@@ -764,6 +848,20 @@ __global__ void __launch_bounds__(2 * kJcLen) jacobi_svd_cluster_kernel(const fl
         }
     }
     cluster.sync();                                           // nobody leaves while a neighbour could still store into it
+}
+
+// Launch configuration of the cluster kernel: one cluster of kJcCtas CTAs, `lanes` threads per pair slot.
+void jacobi_cluster_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, int k, int lanes, cudaStream_t st) {
+    cfg->gridDim = dim3(kJcCtas, 1, 1);
+    cfg->blockDim = dim3(jacobi_cluster_len(k) / 2 * lanes, 1, 1);
+    cfg->dynamicSmemBytes = jacobi_cluster_smem_bytes(k);
+    cfg->stream = st;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kJcCtas;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg->attrs = attr;
+    cfg->numAttrs = 1;
 }
 
 bool alloc_f(float **p, size_t count) {
@@ -885,11 +983,16 @@ SvdWorkspace *svd_workspace_create_sharded(int m, int n, int k, int niter, int s
     if (ok && ws->own_core_svd && ws->k <= kJacobiSingleMaxK)
         ok = cudaFuncSetAttribute(jacobi_svd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)jacobi_smem_bytes(ws->k)) == cudaSuccess;
-    if (ok && ws->own_core_svd && ws->k > kJacobiSingleMaxK)
-        ok = (ws->k <= 128 ? cudaFuncSetAttribute(jacobi_svd_cluster_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                  (int)jacobi_cluster_smem_bytes(ws->k))
-                           : cudaFuncSetAttribute(jacobi_svd_cluster_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                  (int)jacobi_cluster_smem_bytes(ws->k))) == cudaSuccess;
+    if (ok && ws->own_core_svd && ws->k > kJacobiSingleMaxK) {
+        const char *e = getenv("BSQ_JACOBI_LPP");
+        ws->jc_lanes = ws->k <= 128 || (e && atoi(e) == 4) ? 4 : 2;
+        ok = (ws->k <= 128        ? cudaFuncSetAttribute(jacobi_svd_cluster_kernel<128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                         (int)jacobi_cluster_smem_bytes(ws->k))
+              : ws->jc_lanes == 4 ? cudaFuncSetAttribute(jacobi_svd_cluster_kernel<256, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                         (int)jacobi_cluster_smem_bytes(ws->k))
+                                  : cudaFuncSetAttribute(jacobi_svd_cluster_kernel<256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                         (int)jacobi_cluster_smem_bytes(ws->k))) == cudaSuccess;
+    }
     if (ok && ws->k <= kCholeskyBlockedMaxK)
         ok = cudaFuncSetAttribute(cholesky_inverse_blocked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)cholesky_blocked_smem_bytes(ws->k)) == cudaSuccess;
@@ -974,21 +1077,14 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
     // The row-major C read as column-major is C^T = Vc S Uc^T: the solver's "U" is Vc, its "V" is Uc.
     if (ws->own_core_svd && k > kJacobiSingleMaxK) {
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(kJcCtas, 1, 1);
-        cfg.blockDim = dim3(2 * jacobi_cluster_len(k), 1, 1);
-        cfg.dynamicSmemBytes = jacobi_cluster_smem_bytes(k);
-        cfg.stream = st;
         cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = kJcCtas;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        jacobi_cluster_config(&cfg, attr, k, ws->jc_lanes, st);
         const float *core = ws->core;
         float *vc = ws->vc, *uc = ws->uc;
-        err = k <= 128 ? cudaLaunchKernelEx(&cfg, jacobi_svd_cluster_kernel<128>, core, k, d_S, vc, uc)
-                       : cudaLaunchKernelEx(&cfg, jacobi_svd_cluster_kernel<256>, core, k, d_S, vc, uc);
+        unsigned *status = ws->status;
+        err = k <= 128            ? cudaLaunchKernelEx(&cfg, jacobi_svd_cluster_kernel<128, 4>, core, k, d_S, vc, uc, status)
+              : ws->jc_lanes == 4 ? cudaLaunchKernelEx(&cfg, jacobi_svd_cluster_kernel<256, 4>, core, k, d_S, vc, uc, status)
+                                  : cudaLaunchKernelEx(&cfg, jacobi_svd_cluster_kernel<256, 2>, core, k, d_S, vc, uc, status);
         if (err != cudaSuccess) return err;
     } else if (ws->own_core_svd) {
         jacobi_svd_kernel<<<1, 512, jacobi_smem_bytes(k), st>>>(ws->core, k, d_S, ws->vc, ws->uc);
