@@ -193,6 +193,16 @@ cudaError_t launch_reduce(const float *workspace, float *C, int M, int N, long l
     return cudaGetLastError();
 }
 
+// BSQ_GEMM_IMAGE=0 keeps the tensor-core kernel that splits B inside every CTA, =2 uses the kernel with B split
+// beforehand wherever it can run (for A/B comparisons and tests); default 1: where it is faster.
+int b_image_mode() {
+    static const int mode = [] {
+        const char *e = std::getenv("BSQ_GEMM_IMAGE");
+        return e && e[0] >= '0' && e[0] <= '2' ? e[0] - '0' : 1;
+    }();
+    return mode;
+}
+
 // BSQ_GEMM_TC=0 keeps every product on the FP32 pipes (for A/B comparisons of the two kernels).
 bool tensor_cores_enabled() {
     static const bool on = [] {
@@ -229,13 +239,23 @@ cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, c
         t.n_tile = N <= 256 ? N : 128;
         t.flag = minuend ? flag : nullptr;
         const int tiles_tc = ((M + 127) / 128) * ((N + t.n_tile - 1) / t.n_tile);
+        // B split beforehand when several row tiles share it and the workspace has room for its images (at its end)
+        const size_t image_bytes = gemm_tc_image_bytes(N, t.n_tile, K);
+        // (measured: the products are then bound by what the CTAs draw from L2, A once and B's images once per row
+        // tile; that pays for tiles wider than 128 columns, where splitting B in every CTA is two thirds of the
+        // staging work, and for long K)
+        const bool with_image = workspace && image_bytes + 128 <= workspace_bytes &&
+                                (b_image_mode() == 2 ? M >= 256 : (b_image_mode() == 1 && M >= 512 && t.n_tile > 128 && K >= 1024));
+        if (with_image) workspace_bytes = (workspace_bytes - image_bytes) & ~(size_t)127;
         int splits_tc = 1;
-        const int slots = (t.n_tile <= 128 ? 2 : 1) * sm_count;
+        const int slots = (with_image ? gemm_tc_image_ctas_per_sm(t.n_tile) : (t.n_tile <= 128 ? 2 : 1)) * sm_count;
+        if (with_image) gemm_tc_image_rings(t.n_tile, &t.a_stages, &t.b_stages);
         if (workspace && !minuend && !kscale && tiles_tc < slots) {
             const int max_by_k = max(1, K / 64);
             const int max_by_ws = (int)(workspace_bytes / ((size_t)M * N * sizeof(float)));
             splits_tc = max(1, min(slots / tiles_tc, min(max_by_k, max_by_ws)));
         }
+        if (with_image) t.b_image = reinterpret_cast<const float4 *>(reinterpret_cast<unsigned char *>(workspace) + workspace_bytes);
         t.splits = splits_tc;
         t.k_per_split = ((K + splits_tc - 1) / splits_tc + 31) / 32 * 32;
         t.splits = (K + t.k_per_split - 1) / t.k_per_split;                    // no empty split

@@ -20,12 +20,19 @@ struct GemmArgs {
     long ldm;
     unsigned *flag;            // nullable: |= 1 when some |C| > FLT_EPSILON (with minuend)
     int n_tile;                // tensor-core kernel: columns per CTA (a multiple of 16, <= 256); grid.y tiles N
+    const float4 *b_image;     // tensor-core kernel, nullable: room for B split beforehand (gemm_tc_image_bytes, 128-byte aligned)
+    int a_stages, b_stages;    // with b_image: ring lengths in shared memory (gemm_tc_image_rings)
 };
 
 // Tensor-core path: true if the shape qualifies (N a multiple of 16, 16-byte aligned operands with leading
 // dimensions that are multiples of 4; the fused scale / minuend epilogue only without K splits).  Launches with
 // grid (M tiles, N tiles, splits).
 bool gemm_tc_eligible(const GemmArgs &g, bool a_kmajor, bool b_kmajor);
+// With g.b_image set, B is first split into per-chunk hi / lo images there (one small kernel) and the product kernel
+// fetches them by bulk copies; gemm_tc_image_bytes is the room that takes.
+size_t gemm_tc_image_bytes(int N, int n_tile, int K);
+int gemm_tc_image_ctas_per_sm(int n_tile);
+void gemm_tc_image_rings(int n_tile, int *sa, int *nb);
 cudaError_t gemm_tc_launch(const GemmArgs &g, bool a_kmajor, bool b_kmajor, unsigned *status, cudaStream_t stream);
 
 }  // namespace bsq

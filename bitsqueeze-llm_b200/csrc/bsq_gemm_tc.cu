@@ -26,6 +26,8 @@
 #include "bsq_device.cuh"
 #include "bsq_gemm.hpp"
 
+#include <cstdlib>
+
 namespace bsq {
 namespace {
 
@@ -198,6 +200,54 @@ __device__ __forceinline__ uint64_t kstep_desc(unsigned stage_addr, int ks, int 
     return smem_desc(stage_addr + (unsigned)(ks * 2) * lbo_units(extent) * 16u, lbo_units(extent) * 16u, 144u);
 }
 
+// Epilogue of both product kernels, for warps 0-7: accumulator row 32 (warp % 4) + lane; warps 0-3 take the lower half
+// of the columns, warps 4-7 the upper half.  Adds the two accumulators and writes C (or minuend - product).
+__device__ __forceinline__ void tile_epilogue(const GemmArgs &g, unsigned tmem_d, unsigned acc_cols, int chunks, bool ok, int m0, int n0,
+                                              int N, int warp, int tid) {
+    float *C = g.C + (long)blockIdx.z * g.split_stride;
+    const int row = m0 + (warp & 3) * 32 + (tid & 31);
+    const int half = (N / 16 + 1) / 2 * 16;                  // columns of the lower half, a multiple of 16
+    const int c_begin = warp < 4 ? 0 : half, c_end = warp < 4 ? half : N;
+    bool any = false;
+    if (ok) {
+        for (int c0 = c_begin; c0 < c_end; c0 += 16) {
+            unsigned r[16], q[16];
+            if (chunks > 0) {
+                const unsigned taddr = tmem_d + ((unsigned)((warp & 3) * 32) << 16) + (unsigned)c0;
+                tmem_ld16(taddr, r);
+                tmem_ld16(taddr + acc_cols, q);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(q[j])));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[j] = 0u;
+            }
+            if (row < g.M) {
+                float4 *dst = reinterpret_cast<float4 *>(C + (long)row * g.ldc + n0 + c0);
+                if (g.minuend) {                             // C = minuend - product, note whether anything is left
+                    const float4 *mn = reinterpret_cast<const float4 *>(g.minuend + (long)row * g.ldm + n0 + c0);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float4 m4 = mn[j];
+                        const float4 o = make_float4(__fsub_rn(m4.x, __uint_as_float(r[4 * j])), __fsub_rn(m4.y, __uint_as_float(r[4 * j + 1])),
+                                                     __fsub_rn(m4.z, __uint_as_float(r[4 * j + 2])), __fsub_rn(m4.w, __uint_as_float(r[4 * j + 3])));
+                        any |= fabsf(o.x) > 1.1920928955078125e-07f || fabsf(o.y) > 1.1920928955078125e-07f ||
+                               fabsf(o.z) > 1.1920928955078125e-07f || fabsf(o.w) > 1.1920928955078125e-07f;
+                        dst[j] = o;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                                             __uint_as_float(r[4 * j + 3]));
+                }
+            }
+        }
+    }
+    if (g.flag && __any_sync(0xffffffffu, any) && (tid & 31) == 0) atomicOr(g.flag, 1u);
+}
+
 template <bool A_KMAJOR, bool B_KMAJOR, int NMAX>
 __global__ void __launch_bounds__(NT) gemm_tc_kernel(GemmArgs g, unsigned *status) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -317,52 +367,311 @@ __global__ void __launch_bounds__(NT) gemm_tc_kernel(GemmArgs g, unsigned *statu
             }
         }
     }
-    // epilogue: accumulator row 32 (w % 4) + lane; warps 0-3 take the lower half of the columns, warps 4-7 the upper
     if (chunks > 0 && ok) ok = mbar_wait_bounded(&bar_done, 0, status);
     ok = __syncthreads_and(ok) != 0;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    float *C = g.C + (long)blockIdx.z * g.split_stride;
-    const int row = m0 + (warp & 3) * 32 + (tid & 31);
-    const int half = (N / 16 + 1) / 2 * 16;                  // columns of the lower half, a multiple of 16
-    const int c_begin = warp < 4 ? 0 : half, c_end = warp < 4 ? half : N;
-    bool any = false;
-    if (ok) {
-        for (int c0 = c_begin; c0 < c_end; c0 += 16) {
-            unsigned r[16], q[16];
-            if (chunks > 0) {
-                const unsigned taddr = tmem_d + ((unsigned)((warp & 3) * 32) << 16) + (unsigned)c0;
-                tmem_ld16(taddr, r);
-                tmem_ld16(taddr + acc_cols, q);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    tile_epilogue(g, tmem_d, acc_cols, chunks, ok, m0, n0, N, warp, tid);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The same product with the B operand split beforehand.  In the kernel above every CTA splits its B chunk again
+// although all CTAs of a tile column use the same values, and half (N = 128) or two thirds (N = 256) of the staging
+// instructions go into that.  Here one small kernel writes, once per product, the hi / lo images of B exactly as a
+// stage of shared memory wants them (per 16 of K and tile column: [B hi | B lo] in the padded K-major layout), and
+// the product kernel fetches one image per chunk with a single bulk copy (TMA, 1-D) that counts off on an mbarrier.
+// All 256 staging threads then serve A, half a slot each; a ninth warp does nothing but issue the MMAs (one lane:
+// wait for the chunk's image, six MMAs from descriptors that differ from precomputed ones by an addition, one
+// commit), because that chain of dependent instructions is what bounds the time per chunk.  B images have a ring of
+// their own (NB stages): a copy takes longer than one chunk's MMAs.  Staging thread 0 starts a copy as soon as it
+// has seen the MMAs of two chunks ago finish, which is also what frees that chunk's image.
+constexpr int NT2 = NT + 32;     // 8 staging / epilogue warps + the control warp
+constexpr int IMG_DEPTH_2CTA = 3, IMG_DEPTH_1CTA = 3;
+constexpr int MAX_RING = 8;      // most stages of A, and most images of B, in shared memory
+
+// Half of a Slot: two 16-byte units of the operand stage per chunk.
+//   K-major source: k quad kq of two rows (64 contiguous bytes per four neighbouring threads, as in Slot);
+//   MN-major source: 2 consecutive MN indices x 4 consecutive k (four 8-byte loads), transposed in registers.
+struct HalfItem {
+    float2 v[4];
+};
+
+template <bool KMAJOR>
+struct HalfSlot {
+    const float *src;
+    long step;
+    long off[KMAJOR ? 2 : 4];
+    unsigned unit[2];
+    int kq;
+
+    __device__ __forceinline__ void init(const float *P, long ld, int mn_total, int mn0, int k_begin, int extent, int hs) {
+        if (KMAJOR) {
+            const int s = hs % extent, h = hs / extent;       // slot of the full scheme and which half of its rows
+            kq = s % 4;
+            const int r0 = s / 4, rstep = extent / 4;
+            src = P + k_begin + kq * 4;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(q[j])));
-            } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) r[j] = 0u;
+            for (int j = 0; j < 2; ++j) {
+                unit[j] = unit_index(kq, r0 + (2 * h + j) * rstep, extent);
+                off[j] = (long)min(mn0 + r0 + (2 * h + j) * rstep, mn_total - 1) * ld;
             }
-            if (row < g.M) {
-                float4 *dst = reinterpret_cast<float4 *>(C + (long)row * g.ldc + n0 + c0);
-                if (g.minuend) {                             // C = minuend - product, note whether anything is left
-                    const float4 *mn = reinterpret_cast<const float4 *>(g.minuend + (long)row * g.ldm + n0 + c0);
+            step = TK;
+        } else {
+            const int e2 = extent / 2;
+            const int mn2 = hs % e2;
+            kq = hs / e2;
+            const int gmn = mn0 + mn2 * 2;
+            src = P + (long)(k_begin + kq * 4) * ld + (gmn < mn_total ? gmn : 0);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float4 m4 = mn[j];
-                        const float4 o = make_float4(__fsub_rn(m4.x, __uint_as_float(r[4 * j])), __fsub_rn(m4.y, __uint_as_float(r[4 * j + 1])),
-                                                     __fsub_rn(m4.z, __uint_as_float(r[4 * j + 2])), __fsub_rn(m4.w, __uint_as_float(r[4 * j + 3])));
-                        any |= fabsf(o.x) > 1.1920928955078125e-07f || fabsf(o.y) > 1.1920928955078125e-07f ||
-                               fabsf(o.z) > 1.1920928955078125e-07f || fabsf(o.w) > 1.1920928955078125e-07f;
-                        dst[j] = o;
+            for (int j = 0; j < 4; ++j) off[j] = (long)j * ld;
+            unit[0] = unit_index(kq, mn2 * 2, extent);
+            unit[1] = unit_index(kq, mn2 * 2 + 1, extent);
+            step = (long)TK * ld;
+        }
+    }
+    __device__ __forceinline__ void load(HalfItem &it, int c) const {
+        const float *p = src + (long)c * step;
+        if (KMAJOR) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float4 v = *reinterpret_cast<const float4 *>(p + off[j]);
+                it.v[2 * j] = make_float2(v.x, v.y);
+                it.v[2 * j + 1] = make_float2(v.z, v.w);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) it.v[j] = *reinterpret_cast<const float2 *>(p + off[j]);
+        }
+    }
+    __device__ __forceinline__ void load_checked(HalfItem &it, int c, int k_left) const {
+        const float *p = src + (long)c * step;
+        if (KMAJOR) {
+            const int left = k_left - kq * 4;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (left >= 4) v = *reinterpret_cast<const float4 *>(p + off[j]);
+                else if (left > 0) { v.x = p[off[j]]; if (left > 1) v.y = p[off[j] + 1]; if (left > 2) v.z = p[off[j] + 2]; }
+                it.v[2 * j] = make_float2(v.x, v.y);
+                it.v[2 * j + 1] = make_float2(v.z, v.w);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                it.v[j] = kq * 4 + j < k_left ? *reinterpret_cast<const float2 *>(p + off[j]) : make_float2(0.f, 0.f);
+        }
+    }
+    __device__ __forceinline__ void scale(HalfItem &it, const float *sc, int k_left) const {
+        float f[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) f[q] = kq * 4 + q < k_left ? sc[kq * 4 + q] : 0.0f;
+        if (KMAJOR) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                it.v[2 * j].x *= f[0]; it.v[2 * j].y *= f[1]; it.v[2 * j + 1].x *= f[2]; it.v[2 * j + 1].y *= f[3];
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { it.v[j].x *= f[j]; it.v[j].y *= f[j]; }
+        }
+    }
+    __device__ __forceinline__ void store(const HalfItem &it, float4 *hi, float4 *lo) const {
+        if (KMAJOR) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+                split_store(make_float4(it.v[2 * j].x, it.v[2 * j].y, it.v[2 * j + 1].x, it.v[2 * j + 1].y), hi + unit[j], lo + unit[j]);
+        } else {
+            split_store(make_float4(it.v[0].x, it.v[1].x, it.v[2].x, it.v[3].x), hi + unit[0], lo + unit[0]);
+            split_store(make_float4(it.v[0].y, it.v[1].y, it.v[2].y, it.v[3].y), hi + unit[1], lo + unit[1]);
+        }
+    }
+};
+
+// A B image is dense (nobody stores into it with a pattern that could conflict): core matrices of 8 columns x 16 B
+// follow one another along N every 128 B (SBO) and along K every extent * 16 B (LBO).
+__host__ __device__ constexpr unsigned image_half_units(int extent) { return (unsigned)(TK / 4) * (unsigned)extent; }
+__device__ __forceinline__ unsigned image_unit_index(int kc, int r, int extent) { return (unsigned)kc * (unsigned)extent + (unsigned)r; }
+// 16-byte units from one chunk's image to the next, and from one tile column's images to the next
+__host__ __device__ constexpr size_t image_units(int n_tile) { return 2 * (size_t)image_half_units(n_tile); }
+
+// One thread per (chunk, k quad, column): the four values B(16 c + 4 kc .. + 3, n0 + r) split into the hi and the lo
+// unit of the chunk's image.  k past K gives zeros.
+template <bool B_KMAJOR>
+__global__ void __launch_bounds__(256) presplit_b_kernel(const float *__restrict__ B, long ldb, int N, int K, int n_tile, int chunks,
+                                                         float4 *__restrict__ image) {
+    const int n0 = blockIdx.y * n_tile;
+    const int Nt = min(n_tile, N - n0);
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)chunks * 4 * Nt) return;
+    int kc, r;
+    long c;
+    if (B_KMAJOR) {                                           // four neighbouring threads read 64 contiguous bytes
+        kc = (int)(idx % 4);
+        r = (int)((idx / 4) % Nt);
+    } else {                                                  // neighbouring threads read neighbouring columns
+        r = (int)(idx % Nt);
+        kc = (int)((idx / Nt) % 4);
+    }
+    c = idx / (4 * Nt);
+    const long k = c * TK + kc * 4;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (B_KMAJOR) {
+        const float *p = B + (long)(n0 + r) * ldb + k;
+        if (k + 3 < K) {
+            const float4 q = *reinterpret_cast<const float4 *>(p);
+            v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (k + j < K) v[j] = p[j];
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (k + j < K) v[j] = B[(k + j) * ldb + n0 + r];
+    }
+    float4 *img = image + ((size_t)blockIdx.y * chunks + c) * image_units(n_tile);
+    const unsigned u = image_unit_index(kc, r, Nt);
+    split_store(make_float4(v[0], v[1], v[2], v[3]), img + u, img + image_half_units(Nt) + u);
+}
+
+template <bool A_KMAJOR, int NMAX>
+__global__ void __launch_bounds__(NT2, NMAX <= 128 ? 2 : 1) gemm_tc_image_kernel(GemmArgs g, unsigned *status) {
+    // chunks of A in flight in registers per thread: what is in flight per SM is what bounds these products (the
+    // pieces of A are small and far apart in HBM), so as many as the registers of 2 CTAs (N <= 128) or 1 CTA hold
+    constexpr int DEPTH = NMAX <= 128 ? IMG_DEPTH_2CTA : IMG_DEPTH_1CTA;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bar_free[MAX_RING];       // A stage may be overwritten (MMAs that read it are done)
+    __shared__ __align__(8) uint64_t bar_b_full[MAX_RING];          // B image has landed
+    __shared__ __align__(8) uint64_t bar_done;
+    __shared__ unsigned tmem_base_slot;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const bool control = warp == NT / 32;                     // the ninth warp; its lane 0 does the work
+    const int n0 = blockIdx.y * g.n_tile;
+    const int N = min(g.n_tile, g.N - n0);
+    const int m0 = blockIdx.x * TM;
+    const int k_begin = blockIdx.z * g.k_per_split;
+    const int k_end = min(g.K, k_begin + g.k_per_split);
+    const unsigned a_units = stage_units(TM), b_units = image_half_units(N);
+    const unsigned a_stage_bytes = 2 * a_units * 16u, b_stage_bytes = 2 * b_units * 16u;
+    const int SA = g.a_stages, NB = g.b_stages;               // ring lengths: A stages, B images (NB > SA: the copies' head start)
+    unsigned char *b_stages = smem_raw + (size_t)SA * a_stage_bytes;
+    const unsigned acc_cols = N <= 16 ? 16u : (N <= 32 ? 32u : (N <= 64 ? 64u : (N <= 128 ? 128u : 256u)));
+    const unsigned tmem_cols = 2u * acc_cols;
+
+    if (tid == 0) {
+        for (int i = 0; i < SA; ++i) mbar_init(&bar_free[i], 1);
+        for (int i = 0; i < NB; ++i) mbar_init(&bar_b_full[i], 1);
+        mbar_init(&bar_done, 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                     "r"(tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_d = tmem_base_slot;
+    const unsigned idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned)(N >> 3) << 17) | ((unsigned)(TM >> 4) << 24);
+
+    const int chunks = (k_end - k_begin + TK - 1) / TK;
+    const int chunks_total = (g.K + TK - 1) / TK;
+    const float4 *image = g.b_image + ((size_t)blockIdx.y * chunks_total + k_begin / TK) * image_units(g.n_tile);
+    const bool lane0 = control && (tid & 31) == 0;
+    int issued = 0;                                           // thread 0: B copies started
+    auto fetch_b = [&](int c) {                               // thread 0: image of chunk c into its ring stage
+        uint64_t *bar = &bar_b_full[c % NB];
+        mbar_expect_tx(bar, b_stage_bytes);
+        bulk_g2s(b_stages + (size_t)(c % NB) * b_stage_bytes, image + (size_t)c * image_units(g.n_tile), b_stage_bytes, bar);
+        ++issued;
+    };
+    if (tid == 0)
+        for (int c = 0; c < NB && c < chunks; ++c) fetch_b(c);
+    // descriptors of stage 0, k-step 0 (hi); the others differ in the address field only, by whole 16-byte units
+    const uint64_t desc_a0 = smem_desc(smem_u32(smem_raw), lbo_units(TM) * 16u, 144u);
+    const uint64_t desc_b0 = smem_desc(smem_u32(b_stages), (unsigned)N * 16u, 128u);
+    const unsigned a_kstep = 2 * lbo_units(TM), b_kstep = 2u * (unsigned)N;          // units from one 8-wide k-step to the next
+
+    HalfSlot<A_KMAJOR> slot;
+    slot.init(g.A, g.lda, g.M, m0, k_begin, TM, control ? 0 : tid);
+    HalfItem regs[DEPTH];
+    auto load_chunk = [&](HalfItem &r, int c, int k_left) {
+        if (control) return;
+        if (k_left >= TK) {
+            slot.load(r, c);
+            if (g.kscale) slot.scale(r, g.kscale + k_begin + c * TK, TK);
+        } else {
+            slot.load_checked(r, c, k_left);
+            if (g.kscale) slot.scale(r, g.kscale + k_begin + c * TK, k_left);
+        }
+    };
+    bool ok = true, mine = true;                              // mine: this thread's waits so far succeeded
+    unsigned free_phase = 0;
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d)
+        if (d < chunks) load_chunk(regs[d], d, k_end - k_begin - d * TK);
+    for (int c0 = 0; c0 < chunks && ok; c0 += DEPTH) {
+#pragma unroll
+        for (int d = 0; d < DEPTH; ++d) {
+            const int c = c0 + d;
+            if (c < chunks && ok) {                           // uniform over the CTA
+                const int s = c % SA;
+                float4 *a_hi = reinterpret_cast<float4 *>(smem_raw + (size_t)s * a_stage_bytes), *a_lo = a_hi + a_units;
+                if (!control) {
+                    if (c >= SA) {                            // the MMAs of chunk c - SA must be done with stage s
+                        mine = mbar_wait_bounded(&bar_free[s], (free_phase >> s) & 1u, status);
+                        free_phase ^= 1u << s;
+                        // ... and with that chunk's image of B: the next one for its place in the ring can come
+                        if (tid == 0 && mine && c - SA + NB < chunks) fetch_b(c - SA + NB);
                     }
-                } else {
+                    slot.store(regs[d], a_hi, a_lo);
+                    if (c + DEPTH < chunks) load_chunk(regs[d], c + DEPTH, k_end - k_begin - (c + DEPTH) * TK);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                ok = __syncthreads_and(mine) != 0;            // uniform: after a timeout nobody issues or loops on
+                if (lane0 && ok) {
+                    // The stores of all staging threads happen before this point (the CTA barrier); the fence that hands
+                    // them from the generic proxy to the tensor core's (async) proxy is executed here, by the one thread
+                    // that issues the MMAs.  A fence in every staging thread also waits for that thread's global loads
+                    // in flight, which costs a memory latency per chunk.
+                    fence_proxy_async_smem();
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const int sb = c % NB;
+                    mine = mbar_wait_bounded(&bar_b_full[sb], (unsigned)(c / NB) & 1u, status);
+                    if (mine) {
+                        const uint64_t dah0 = desc_a0 + (uint64_t)((unsigned)s * 2u * a_units), dbh0 = desc_b0 + (uint64_t)((unsigned)sb * 2u * b_units);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
-                                             __uint_as_float(r[4 * j + 3]));
+                        for (int ks = 0; ks < TK / 8; ++ks) {
+                            const uint64_t dah = dah0 + (uint64_t)(ks * a_kstep), dal = dah + a_units;
+                            const uint64_t dbh = dbh0 + (uint64_t)(ks * b_kstep), dbl = dbh + b_units;
+                            mma_tf32(tmem_d, dah, dbh, idesc, c > 0 || ks > 0);
+                            mma_tf32(tmem_d + acc_cols, dal, dbh, idesc, c > 0 || ks > 0);
+                            mma_tf32(tmem_d + acc_cols, dah, dbl, idesc, true);
+                        }
+                        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                         smem_u32(c + 1 == chunks ? &bar_done : &bar_free[s]))
+                                     : "memory");
+                    }
                 }
             }
         }
     }
-    if (g.flag && __any_sync(0xffffffffu, any) && (tid & 31) == 0) atomicOr(g.flag, 1u);
+    if (chunks > 0 && ok) ok = mbar_wait_bounded(&bar_done, 0, status);
+    ok = __syncthreads_and(ok && mine) != 0;
+    if (tid == 0 && !ok) {
+        // leaving early: the copies still in flight must have landed before this CTA's shared memory goes away (a
+        // wait for an image that was already used returns at once)
+        for (int c = max(0, issued - NB); c < issued; ++c) mbar_wait_bounded(&bar_b_full[c % NB], (unsigned)(c / NB) & 1u, status);
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (!control) tile_epilogue(g, tmem_d, acc_cols, chunks, ok, m0, n0, N, warp, tid);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) {
@@ -388,7 +697,57 @@ cudaError_t launch(const GemmArgs &g, unsigned *status, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
+// Ring lengths of the image kernel for a tile of N columns: two stages of A and four images of B (two chunks of head
+// start for the copies).  Longer rings (up to 6 + 8, one CTA per SM) measured the same for N = 256 and slower for
+// N = 128, where they cost the second CTA on the SM.  BSQ_TC_SA / BSQ_TC_NB override them for experiments.
+void tc_image_rings(int N, int *sa, int *nb) {
+    static const int env_sa = [] { const char *e = std::getenv("BSQ_TC_SA"); return e ? atoi(e) : 0; }();
+    static const int env_nb = [] { const char *e = std::getenv("BSQ_TC_NB"); return e ? atoi(e) : 0; }();
+    *sa = 2;
+    *nb = 4;
+    if (env_sa >= 2 && env_sa <= MAX_RING && env_nb > env_sa && env_nb <= MAX_RING) {
+        *sa = env_sa;
+        *nb = env_nb;
+    }
+    while (((size_t)*sa * 2 * stage_units(TM) + (size_t)*nb * 2 * image_half_units(N)) * 16 > 226 * 1024 && *sa > 2) {
+        --*sa;
+        --*nb;
+    }
+}
+size_t tc_image_smem_bytes(int N, int sa, int nb) { return ((size_t)sa * 2 * stage_units(TM) + (size_t)nb * 2 * image_half_units(N)) * 16; }
+
+template <bool AK, int NMAX>
+cudaError_t launch_image(const GemmArgs &g, bool b_kmajor, unsigned *status, cudaStream_t stream) {
+    const int chunks = (g.K + TK - 1) / TK, n_tiles = (g.N + g.n_tile - 1) / g.n_tile;
+    float4 *image = const_cast<float4 *>(g.b_image);
+    dim3 pgrid((unsigned)(((long)chunks * 4 * g.n_tile + 255) / 256), n_tiles, 1);
+    if (b_kmajor) presplit_b_kernel<true><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image);
+    else presplit_b_kernel<false><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return err;
+    const size_t smem = tc_image_smem_bytes(g.n_tile, g.a_stages, g.b_stages);
+    err = cudaFuncSetAttribute(gemm_tc_image_kernel<AK, NMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return err;
+    dim3 grid((g.M + TM - 1) / TM, n_tiles, g.splits);
+    gemm_tc_image_kernel<AK, NMAX><<<grid, NT2, smem, stream>>>(g, status);
+    return cudaGetLastError();
+}
+
 }  // namespace
+
+// CTAs of the image kernel that share an SM (tensor memory: 2 x 256 columns up to N = 128; shared memory: the rings)
+int gemm_tc_image_ctas_per_sm(int n_tile) {
+    int sa, nb;
+    tc_image_rings(n_tile, &sa, &nb);
+    const size_t smem = tc_image_smem_bytes(n_tile, sa, nb) + 1024;
+    const int by_smem = (int)((size_t)228 * 1024 / smem), by_tmem = n_tile <= 128 ? 2 : 1;
+    return by_smem < by_tmem ? (by_smem < 1 ? 1 : by_smem) : by_tmem;
+}
+void gemm_tc_image_rings(int n_tile, int *sa, int *nb) { tc_image_rings(n_tile, sa, nb); }
+
+size_t gemm_tc_image_bytes(int N, int n_tile, int K) {
+    return (size_t)((N + n_tile - 1) / n_tile) * ((K + TK - 1) / TK) * image_units(n_tile) * 16;
+}
 
 bool gemm_tc_eligible(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
     (void)a_kmajor;
@@ -404,6 +763,10 @@ bool gemm_tc_eligible(const GemmArgs &g, bool a_kmajor, bool b_kmajor) {
 }
 
 cudaError_t gemm_tc_launch(const GemmArgs &g, bool a_kmajor, bool b_kmajor, unsigned *status, cudaStream_t stream) {
+    if (g.b_image) {                                          // B split beforehand, fetched by bulk copies
+        if (a_kmajor) return g.n_tile <= 128 ? launch_image<true, 128>(g, b_kmajor, status, stream) : launch_image<true, 256>(g, b_kmajor, status, stream);
+        return g.n_tile <= 128 ? launch_image<false, 128>(g, b_kmajor, status, stream) : launch_image<false, 256>(g, b_kmajor, status, stream);
+    }
 #define BSQ_TC(AK, BK)                                                                  \
     (g.n_tile <= 128 ? launch<AK, BK, 128>(g, status, stream) : launch<AK, BK, 256>(g, status, stream))
     if (a_kmajor && b_kmajor) return BSQ_TC(true, true);

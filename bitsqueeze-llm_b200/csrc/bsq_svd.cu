@@ -21,6 +21,7 @@
 // Omega comes from cuRAND's XORWOW generator like the reference's (svd_lowrank_cuda.cu:143,289-291),
 // seeded per call, column-major N x k.
 #include "bsq_device.cuh"
+#include "bsq_gemm.hpp"
 #include "bsq_internal.hpp"
 
 #include <cooperative_groups.h>
@@ -901,7 +902,8 @@ cudaError_t orthonormalise(SvdWorkspace *ws, float *Y, float *tmp, int rows, int
         err = cudaGetLastError();
         if (err != cudaSuccess) return err;
         // dst = src T
-        err = gemm(true, false, src, k, ws->t, k, dst, k, rows, k, k, nullptr, nullptr, 0, nullptr, ws->status, nullptr, 0, ws->sm_count, st);
+        err = gemm(true, false, src, k, ws->t, k, dst, k, rows, k, k, nullptr, nullptr, 0, nullptr, ws->status, ws->gemm_ws,
+                   ws->gemm_ws_bytes, ws->sm_count, st);
         if (err != cudaSuccess) return err;
         std::swap(src, dst);
     }
@@ -953,7 +955,9 @@ SvdWorkspace *svd_workspace_create_sharded(int m, int n, int k, int niter, int s
               alloc_f(&ws->t, kk) && alloc_f(&ws->tinv1, kk) && alloc_f(&ws->tinv2, kk) && alloc_f(&ws->core, kk) &&
               alloc_f(&ws->uc, kk) && alloc_f(&ws->vc, kk);
     // split-K partials: up to 2 * SMs tiles' worth of the largest skinny product, and of the Gram matrix
-    ws->gemm_ws_bytes = std::max((size_t)ws->M * ws->k * 8, kk * 2 * (size_t)sm_count) * sizeof(float);
+    // K-split partials, and behind them room for the images of a product's second operand split beforehand
+    ws->gemm_ws_bytes = std::max((size_t)ws->M * ws->k * 8, kk * 2 * (size_t)sm_count) * sizeof(float) +
+                        gemm_tc_image_bytes(ws->k, ws->k <= 256 ? ws->k : 128, std::max(ws->M, ws->N)) + 256;
     ok = ok && alloc_f(&ws->gemm_ws, ws->gemm_ws_bytes / sizeof(float));
     ok = ok && cudaMalloc(reinterpret_cast<void **>(&ws->dev_info), sizeof(int)) == cudaSuccess;
     ok = ok && cudaMalloc(reinterpret_cast<void **>(&ws->own_status), sizeof(unsigned)) == cudaSuccess;
@@ -1096,10 +1100,10 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
     // W = (Q Vc) S (Q2 Uc)^T; both k x k factors are column-major, i.e. K-major B operands
     float *d_left = ws->transposed ? d_V : d_U;            // M x k factor
     float *d_right = ws->transposed ? d_U : d_V;           // N x k factor
-    if ((err = gemm(true, true, q, k, ws->vc, k, d_left, k, ws->M, k, k, nullptr, nullptr, 0, nullptr, ws->status, nullptr, 0,
+    if ((err = gemm(true, true, q, k, ws->vc, k, d_left, k, ws->M, k, k, nullptr, nullptr, 0, nullptr, ws->status, ws->gemm_ws, ws->gemm_ws_bytes,
                     ws->sm_count, st)) != cudaSuccess)
         return err;
-    return gemm(true, true, qz, k, ws->uc, k, d_right, k, ws->N, k, k, nullptr, nullptr, 0, nullptr, ws->status, nullptr, 0,
+    return gemm(true, true, qz, k, ws->uc, k, d_right, k, ws->N, k, k, nullptr, nullptr, 0, nullptr, ws->status, ws->gemm_ws, ws->gemm_ws_bytes,
                 ws->sm_count, st);
 }
 
