@@ -251,7 +251,7 @@ cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, c
         const int slots = (with_image ? gemm_tc_image_ctas_per_sm(t.n_tile) : (t.n_tile <= 128 ? 2 : 1)) * sm_count;
         if (with_image) gemm_tc_image_rings(t.n_tile, &t.a_stages, &t.b_stages);
         if (workspace && !minuend && !kscale && tiles_tc < slots) {
-            const int max_by_k = max(1, K / 64);
+            const int max_by_k = max(1, K / 256);             // a split below 256 of K costs more in the reduction than it gains
             const int max_by_ws = (int)(workspace_bytes / ((size_t)M * N * sizeof(float)));
             splits_tc = max(1, min(slots / tiles_tc, min(max_by_k, max_by_ws)));
         }
