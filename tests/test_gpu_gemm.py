@@ -38,6 +38,7 @@ def run(lib, a, b, M, N, K, a_kmajor, b_kmajor, tensor_cores, workspace):
 SHAPES = [
     (128, 16, 128), (128, 128, 128), (256, 64, 256), (300, 48, 200), (1000, 128, 1000), (4096, 128, 4096),
     (2048, 256, 1024), (512, 240, 416), (131, 32, 132), (128, 128, 4096),
+    (1024, 160, 2008), (640, 256, 4096),      # B split beforehand: K tail, partial last row tile
     (96, 64, 300),      # fewer rows than a tensor-core tile: FP32 pipes
     (256, 40, 256),     # N not a multiple of 16: FP32 pipes
 ]

@@ -62,7 +62,10 @@ def test_reconstruct_matches_fp64(lib, oracle, shape):
     assert np.allclose(d_out.cpu().numpy(), 0.25, atol=1e-4 * max(1.0, float(np.abs(want).max())))
 
 
-@pytest.mark.parametrize("case", [(1024, 512, 64, 2), (512, 2048, 32, 2), (2048, 1024, 128, 1), (300, 180, 20, 3)])
+@pytest.mark.parametrize("case", [(1024, 512, 64, 2), (512, 2048, 32, 2), (2048, 1024, 128, 1), (300, 180, 20, 3),
+                                  # cores for the cluster Jacobi kernel: below and at its 128 columns, odd, between 128
+                                  # and 256 and at 256 (where the products take the kernel with B split beforehand)
+                                  (1024, 768, 96, 2), (700, 900, 131, 2), (1024, 1024, 160, 2), (1536, 1024, 256, 2)])
 def test_svd_accuracy_against_exact(lib, case):
     m, n, k, niter = case
     a = lowrank_plus_noise(m, n, 2 * k, 1e-3, m + n)
@@ -77,8 +80,16 @@ def test_svd_accuracy_against_exact(lib, case):
     assert np.all(s <= exact[:k] * (1 + 2e-4)) and np.all(s >= 0.75 * exact[:k])
     assert np.max(np.abs(s[:2] - exact[:2]) / exact[:2]) <= 1e-4                  # well-separated leading values
     assert np.max(np.abs(s[:4] - exact[:4]) / exact[:4]) <= (1e-3 if niter >= 2 else 5e-3)
-    assert np.max(np.abs(s[:k // 4] - exact[:k // 4]) / exact[:k // 4]) <= (1e-2 if niter >= 2 else 1e-1)
-    assert np.abs(u.T @ u - np.eye(k)).max() <= 1e-4 and np.abs(v.T @ v - np.eye(k)).max() <= 1e-4
+    # the leading quarter: its last values come close to the noise term's largest singular value, about
+    # 1e-3 (sqrt(m) + sqrt(n)), for the larger ranks, where an FP64 numpy run of the same algorithm (no oversampling)
+    # is 2-4 % off as well
+    quarter_tol = (1e-2 if niter >= 2 else 1e-1) if k <= 64 or niter < 2 else 5e-2
+    assert np.max(np.abs(s[:k // 4] - exact[:k // 4]) / exact[:k // 4]) <= quarter_tol
+    # orthonormal to the shift of the Cholesky QR: each pass factors G + 1e-5 max(diag G) I, which leaves 1 - |q|^2 of
+    # about 1e-5 / (the direction's share of the Gram matrix after the first pass): 1e-5 for most columns, up to
+    # ~1e-4 for the weakest direction of a 256-column sketch
+    orth_tol = 1e-4 if k <= 128 else 2e-4
+    assert np.abs(u.T @ u - np.eye(k)).max() <= orth_tol and np.abs(v.T @ v - np.eye(k)).max() <= orth_tol
 
 
 def test_svd_rank_deficient_and_zero_inputs(lib):
