@@ -996,6 +996,20 @@ SvdWorkspace *svd_workspace_create_sharded(int m, int n, int k, int niter, int s
                                                          (int)jacobi_cluster_smem_bytes(ws->k))
                                   : cudaFuncSetAttribute(jacobi_svd_cluster_kernel<256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                          (int)jacobi_cluster_smem_bytes(ws->k))) == cudaSuccess;
+        if (ok) {
+            // a device (or partition of one) that cannot place a cluster of 8 such CTAs keeps the library solver
+            cudaLaunchConfig_t cfg = {};
+            cudaLaunchAttribute attr[1];
+            jacobi_cluster_config(&cfg, attr, ws->k, ws->jc_lanes, nullptr);
+            int clusters = 0;
+            const cudaError_t q = ws->k <= 128        ? cudaOccupancyMaxActiveClusters(&clusters, jacobi_svd_cluster_kernel<128, 4>, &cfg)
+                                  : ws->jc_lanes == 4 ? cudaOccupancyMaxActiveClusters(&clusters, jacobi_svd_cluster_kernel<256, 4>, &cfg)
+                                                      : cudaOccupancyMaxActiveClusters(&clusters, jacobi_svd_cluster_kernel<256, 2>, &cfg);
+            if (q != cudaSuccess || clusters < 1) {
+                cudaGetLastError();
+                ws->own_core_svd = false;
+            }
+        }
     }
     if (ok && ws->k <= kCholeskyBlockedMaxK)
         ok = cudaFuncSetAttribute(cholesky_inverse_blocked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
