@@ -125,7 +125,8 @@ int bsq_reconstruct(const float *d_U, const float *d_S, const float *d_V, int m,
 /* The FP32 matrix product inside the two stages above, where the reference calls cublasSgemm
  * (svd_lowrank_cuda.cu:293-309, reconstruct_lowrank_cuda.cu:46-61): C[M x N] = opA[M x K] * opB[K x N], all row-major
  * device arrays.  a_kmajor: opA(i,kk) = A[i*lda+kk], else A[kk*lda+i]; b_kmajor: opB(kk,j) = B[j*ldb+kk], else B[kk*ldb+j].
- * d_workspace (nullable) allows a deterministic split of K.  allow_tensor_cores = 0 keeps the product on the FP32 pipes;
+ * d_workspace (nullable) allows a deterministic split of K and, above 128 columns, holds opB split once into the
+ * tensor cores' operand format (room for 8 K N bytes makes that possible).  allow_tensor_cores = 0 keeps the product on the FP32 pipes;
  * otherwise products with N a multiple of 16 up to 256 run as 3xTF32 on the tensor cores (FP32-level accuracy).
  * d_status (nullable) receives bit 0 if a bounded wait inside the tensor-core kernel gave up.  Exported so that the
  * kernel can be tested and timed on its own. */
