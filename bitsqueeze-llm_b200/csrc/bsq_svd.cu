@@ -244,32 +244,62 @@ __host__ __device__ constexpr size_t cholesky_blocked_smem_bytes(int k) {
 }
 __device__ __forceinline__ int blk_id(int I, int J, int nb) { return I * nb - (I * (I - 1)) / 2 + (J - I); }
 
-// Four 32 x 32 block products at a time: a quarter of the CTA (256 threads) per product, 2 x 2 outputs per thread
-// (rows 2 ti, 2 ti + 1, columns 2 tc, 2 tc + 1), operands read as float2.
+// Sixteen 32 x 32 block products at a time: 64 threads per product, 4 x 4 outputs per thread (rows 4 ti .. + 3,
+// columns 4 tc .. + 3), operands read as float4: 2 shared-memory loads per 16 multiply-adds (with 2 x 2 outputs
+// per thread the loads, not the arithmetic, filled the issue slots of the one SM this kernel runs on).
 //   out -= A^T B  (AT = true:  A, B hold the contraction index in rows)
 //   out += A B    (AT = false: A holds it in columns)
 template <bool AT>
-__device__ __forceinline__ void block_mac(float (&acc)[2][2], const float *__restrict__ A, const float *__restrict__ B, int ti, int tc) {
-#pragma unroll 8
-    for (int l = 0; l < kCB; ++l) {
-        const float2 b = *reinterpret_cast<const float2 *>(B + l * kCB + 2 * tc);
-        float a0, a1;
-        if (AT) {
-            const float2 a = *reinterpret_cast<const float2 *>(A + l * kCB + 2 * ti);
-            a0 = -a.x;
-            a1 = -a.y;
-        } else {
-            a0 = A[(2 * ti) * kCB + l];
-            a1 = A[(2 * ti + 1) * kCB + l];
+__device__ __forceinline__ void block_mac(float (&acc)[4][4], const float *__restrict__ A, const float *__restrict__ B, int ti, int tc) {
+    if (AT) {
+#pragma unroll 4
+        for (int l = 0; l < kCB; ++l) {
+            const float4 a = *reinterpret_cast<const float4 *>(A + l * kCB + 4 * ti);
+            const float4 b = *reinterpret_cast<const float4 *>(B + l * kCB + 4 * tc);
+            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) acc[r][q] = fmaf(-av[r], bv[q], acc[r][q]);
         }
-        acc[0][0] += a0 * b.x; acc[0][1] += a0 * b.y;
-        acc[1][0] += a1 * b.x; acc[1][1] += a1 * b.y;
+    } else {
+#pragma unroll 2
+        for (int l0 = 0; l0 < kCB; l0 += 4) {
+            float4 a[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) a[r] = *reinterpret_cast<const float4 *>(A + (4 * ti + r) * kCB + l0);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float4 b = *reinterpret_cast<const float4 *>(B + (l0 + u) * kCB + 4 * tc);
+                const float bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const float ar = u == 0 ? a[r].x : (u == 1 ? a[r].y : (u == 2 ? a[r].z : a[r].w));
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) acc[r][q] += ar * bv[q];
+                }
+            }
+        }
     }
+}
+// a thread's 4 x 4 tile of a block, as four float4
+__device__ __forceinline__ void tile_load(float (&acc)[4][4], const float *O, int ti, int tc) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const float4 v = *reinterpret_cast<const float4 *>(O + (4 * ti + r) * kCB + 4 * tc);
+        acc[r][0] = v.x; acc[r][1] = v.y; acc[r][2] = v.z; acc[r][3] = v.w;
+    }
+}
+__device__ __forceinline__ void tile_store(const float (&acc)[4][4], float *O, int ti, int tc, float sign) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+        *reinterpret_cast<float4 *>(O + (4 * ti + r) * kCB + 4 * tc) =
+            make_float4(sign * acc[r][0], sign * acc[r][1], sign * acc[r][2], sign * acc[r][3]);
 }
 
 __global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const float *__restrict__ G, int k, float *__restrict__ T,
                                                                         float *__restrict__ Rcpy) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     const int nb = chol_blocks(k), nbt = nb * (nb + 1) / 2;
     float *blocks = sm;                                    // nbt blocks of 32 x 32, row-major
     float *tinv = blocks + (size_t)nbt * kCB * kCB;        // nb inverted diagonal blocks
@@ -278,7 +308,7 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const fl
     float *red = dinv + nb * kCB;                          // 32 + 1
     const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
     const int bi = tid >> 5, bc = tid & 31;               // this thread's element of a block when the CTA walks blocks
-    const int quarter = tid >> 8, ti = (tid & 255) >> 4, tc = tid & 15;   // ... and its 2 x 2 tile of a quarter's block
+    const int part = tid >> 6, ti = (tid & 63) >> 3, tc = tid & 7;         // ... and its 4 x 4 tile of its sixteenth's block
     // load block by block (row bi, column bc of each), padded with an identity; what lies below the diagonal of a
     // diagonal block is never read.  Four blocks per trip, so that four global loads are in flight per thread.
     float md = 0.0f;
@@ -362,11 +392,11 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const fl
             for (int i = 0; i < kCB; ++i) X[i * kCB] = y[i];
         }
         __syncthreads();
-        // trailing blocks (A, B), J < A <= B: G_AB -= R_JA^T R_JB, four blocks per trip
+        // trailing blocks (A, B), J < A <= B: G_AB -= R_JA^T R_JB, sixteen blocks per trip
         {
             const int rest = nb - J - 1, pairs = rest * (rest + 1) / 2;
-            for (int pr0 = 0; pr0 < pairs; pr0 += 4) {
-                const int pr = pr0 + quarter;
+            for (int pr0 = 0; pr0 < pairs; pr0 += 16) {
+                const int pr = pr0 + part;
                 if (pr < pairs) {
                     int A = 0, rem = pr;
                     while (rem >= rest - A) { rem -= rest - A; ++A; }
@@ -374,12 +404,10 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const fl
                     const float *RA = blocks + (size_t)blk_id(J, J + 1 + A, nb) * kCB * kCB;
                     const float *RB = blocks + (size_t)blk_id(J, J + 1 + B, nb) * kCB * kCB;
                     float *O = blocks + (size_t)blk_id(J + 1 + A, J + 1 + B, nb) * kCB * kCB;
-                    float2 *o0 = reinterpret_cast<float2 *>(O + (2 * ti) * kCB + 2 * tc);
-                    float2 *o1 = reinterpret_cast<float2 *>(O + (2 * ti + 1) * kCB + 2 * tc);
-                    float acc[2][2] = {{o0->x, o0->y}, {o1->x, o1->y}};
+                    float acc[4][4];
+                    tile_load(acc, O, ti, tc);
                     block_mac<true>(acc, RA, RB, ti, tc);
-                    *o0 = make_float2(acc[0][0], acc[0][1]);
-                    *o1 = make_float2(acc[1][0], acc[1][1]);
+                    tile_store(acc, O, ti, tc, 1.0f);
                 }
             }
         }
@@ -420,29 +448,25 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const fl
     __syncthreads();
     // block column J of T, from the left: needs T_IL for L < J (already in place) and R_LJ (still in place)
     for (int J = 1; J < nb; ++J) {
-        for (int I0 = 0; I0 < J; I0 += 4) {
-            const int I = I0 + quarter;
+        for (int I0 = 0; I0 < J; I0 += 16) {
+            const int I = I0 + part;
             if (I < J) {
-                float acc[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
+                float acc[4][4] = {};
                 for (int L = I; L < J; ++L) {
                     const float *TL = (L == I) ? tinv + (size_t)I * kCB * kCB : blocks + (size_t)blk_id(I, L, nb) * kCB * kCB;
                     block_mac<false>(acc, TL, blocks + (size_t)blk_id(L, J, nb) * kCB * kCB, ti, tc);
                 }
-                float *O = tmp + (size_t)I * kCB * kCB;
-                *reinterpret_cast<float2 *>(O + (2 * ti) * kCB + 2 * tc) = make_float2(acc[0][0], acc[0][1]);
-                *reinterpret_cast<float2 *>(O + (2 * ti + 1) * kCB + 2 * tc) = make_float2(acc[1][0], acc[1][1]);
+                tile_store(acc, tmp + (size_t)I * kCB * kCB, ti, tc, 1.0f);
             }
         }
         __syncthreads();
         const float *TJ = tinv + (size_t)J * kCB * kCB;
-        for (int I0 = 0; I0 < J; I0 += 4) {
-            const int I = I0 + quarter;
+        for (int I0 = 0; I0 < J; I0 += 16) {
+            const int I = I0 + part;
             if (I < J) {
-                float acc[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
+                float acc[4][4] = {};
                 block_mac<false>(acc, tmp + (size_t)I * kCB * kCB, TJ, ti, tc);
-                float *O = blocks + (size_t)blk_id(I, J, nb) * kCB * kCB;
-                *reinterpret_cast<float2 *>(O + (2 * ti) * kCB + 2 * tc) = make_float2(-acc[0][0], -acc[0][1]);
-                *reinterpret_cast<float2 *>(O + (2 * ti + 1) * kCB + 2 * tc) = make_float2(-acc[1][0], -acc[1][1]);
+                tile_store(acc, blocks + (size_t)blk_id(I, J, nb) * kCB * kCB, ti, tc, -1.0f);
             }
         }
         __syncthreads();
