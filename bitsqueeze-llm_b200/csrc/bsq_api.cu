@@ -288,6 +288,7 @@ bool setup_runtime(Runtime &rt, bool compress, uint16_t rows, uint16_t cols, flo
         size_t scratch = nf4dq_scratch_bytes(n);
         scratch = std::max(scratch, frontend_scratch_bytes(rows, cols));
         if (!rt.scratch.alloc(scratch)) return false;
+        if (cudaMemset(rt.scratch.p, 0, 16) != cudaSuccess) return false;      // the front end's carried selection bound starts empty
     }
     rt.initialized = true;
     return true;

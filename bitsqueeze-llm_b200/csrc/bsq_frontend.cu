@@ -53,12 +53,21 @@ __device__ __forceinline__ unsigned stream_next_row(const RowGroup<G> &g, GroupC
     return c.next_row;
 }
 
+// The selection bound that the last launch on this scratch area left behind (a group's first row otherwise has to
+// work one out with a sweep of its own, and a group sees only three or four rows of a 4096-row matrix).  Any value
+// is safe: the bound only says where to look for candidates, a row that finds fewer than k above it (or too many)
+// works out its own; the pairs written never depend on it.
+__device__ __forceinline__ float carried_hint(const unsigned *hint_word) {
+    const float h = __uint_as_float(*hint_word);
+    return (h > 0.0f && h < __int_as_float(0x7f800000)) ? h : 0.0f;
+}
+
 // NF4_DQ kernel 1: selection + block maxima + global maximum.
 template <int G>
 __global__ void __launch_bounds__(256, 4)
     frontend_select_kernel(const float *__restrict__ in, unsigned rows, unsigned cols, unsigned k,
                            uint16_t *__restrict__ out_idx, float *__restrict__ out_val, float *__restrict__ absmax_scratch,
-                           unsigned *gmax_bits, unsigned *row_counter) {
+                           unsigned *gmax_bits, unsigned *row_counter, unsigned *hint_word) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const RowGroup<G> g;
     const StreamLayout lay = stream_layout(cols, 0);
@@ -69,13 +78,14 @@ __global__ void __launch_bounds__(256, 4)
     const unsigned blocks_per_row = cols >> 6;
     unsigned pending = 0;
     if (g.lane == 0) pending = atomicAdd(row_counter, 1u);
-    float run = 0.0f, hint = 0.0f;
+    float run = 0.0f, hint = k > 0 ? carried_hint(hint_word) : 0.0f;
     for (;;) {
         const unsigned r = stream_next_row<G>(g, c, row_counter, pending, rows);
         if (r >= rows) break;
         hint = stream_select_absmax<G>(g, c, blk, bitmap, GlobalRow{in + (size_t)r * cols}, cols, k, out_idx + (size_t)r * k,
                                        out_val + (size_t)r * k, hint, absmax_scratch + (size_t)r * blocks_per_row, &run);
     }
+    if (g.lane == 0 && hint > 0.0f) *hint_word = __float_as_uint(hint);      // whichever group writes last: all are usable
     run = warp_max(run);
     if ((g.lane & 31) == 0 && run > 0.0f) atomicMax(gmax_bits, __float_as_uint(run));
 }
@@ -144,7 +154,7 @@ template <int G>
 __global__ void __launch_bounds__(256, 2)
     frontend_nf4_kernel(const float *__restrict__ in, unsigned rows, unsigned cols, unsigned k, uint16_t *__restrict__ out_idx,
                         float *__restrict__ out_val, float *__restrict__ scales_f32, uint8_t *__restrict__ data,
-                        unsigned *row_counter) {
+                        unsigned *row_counter, unsigned *hint_word) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const RowGroup<G> g;
     const StreamLayout lay = stream_layout(cols, 2);
@@ -159,7 +169,7 @@ __global__ void __launch_bounds__(256, 2)
     unsigned buf = 0;
     unsigned pending = 0;
     if (g.lane == 0) pending = atomicAdd(row_counter, 1u);
-    float run = 0.0f, hint = 0.0f;
+    float run = 0.0f, hint = k > 0 ? carried_hint(hint_word) : 0.0f;
     for (;;) {
         if (g.lane == 0) bulk_wait_read_1();
         const unsigned r = stream_next_row<G>(g, c, row_counter, pending, rows);
@@ -178,6 +188,7 @@ __global__ void __launch_bounds__(256, 2)
         encode_and_store<G>(g, c, row, cols, first, lut, blkf, codes, sel, data + (size_t)r * (cols / 2));
         buf ^= 1u;
     }
+    if (g.lane == 0 && hint > 0.0f) *hint_word = __float_as_uint(hint);
     if (g.lane == 0) bulk_wait_all();
 }
 
@@ -217,11 +228,12 @@ template <int G>
 cudaError_t launch_front(int method, const float *d_in, uint32_t rows, uint32_t cols, uint32_t k, uint16_t *d_idx,
                          float *d_val, float *d_scales_f32, float *d_dq, uint8_t *d_scale_codes, uint8_t *d_data,
                          void *d_scratch, int sm_count, cudaStream_t stream, cudaEvent_t *events) {
-    // scratch words: [0] global maximum, [1] row counter of kernel 1, [2] row counter of kernel 2
+    // scratch words: [0] global maximum, [1] row counter of kernel 1, [2] row counter of kernel 2 (cleared per call),
+    // [3] the selection bound carried from call to call (never cleared; see carried_hint)
     unsigned *gmax = static_cast<unsigned *>(d_scratch);
     float *absmax = reinterpret_cast<float *>(static_cast<uint8_t *>(d_scratch) + 16);
     unsigned grid = 0;
-    cudaError_t err = cudaMemsetAsync(gmax, 0, 16, stream);
+    cudaError_t err = cudaMemsetAsync(gmax, 0, 12, stream);
     if (err != cudaSuccess) return err;
     if (method == 11) {
         const FrontGeometry f = front_geometry(cols, 2);
@@ -229,7 +241,7 @@ cudaError_t launch_front(int method, const float *d_in, uint32_t rows, uint32_t 
         if (err != cudaSuccess) return err;
         if (events) cudaEventRecord(events[0], stream);
         frontend_nf4_kernel<G><<<grid, f.threads, f.smem, stream>>>(d_in, rows, cols, k, d_idx, d_val, d_scales_f32, d_data,
-                                                                    gmax + 1);
+                                                                    gmax + 1, gmax + 3);
         if (events) { cudaEventRecord(events[1], stream); cudaEventRecord(events[2], stream); }
         return cudaGetLastError();
     }
@@ -237,7 +249,8 @@ cudaError_t launch_front(int method, const float *d_in, uint32_t rows, uint32_t 
     err = persistent_grid(frontend_select_kernel<G>, f1.threads, f1.smem, sm_count, rows, f1.groups, &grid);
     if (err != cudaSuccess) return err;
     if (events) cudaEventRecord(events[0], stream);
-    frontend_select_kernel<G><<<grid, f1.threads, f1.smem, stream>>>(d_in, rows, cols, k, d_idx, d_val, absmax, gmax, gmax + 1);
+    frontend_select_kernel<G><<<grid, f1.threads, f1.smem, stream>>>(d_in, rows, cols, k, d_idx, d_val, absmax, gmax, gmax + 1,
+                                                                     gmax + 3);
     err = cudaGetLastError();
     if (err != cudaSuccess) return err;
     if (events) cudaEventRecord(events[1], stream);

@@ -95,6 +95,9 @@ int bsq_nf4dq_dequantize(const float *d_dq, const uint8_t *d_scale_codes, const 
 /* ---- fused outlier separation + quantiser: the no-SVD branch of bitsqz_llm_compress
  * (src/bitsqz_llm.cu:1045-1056,1183-1195) as one stage --------------------------------------- */
 int bsq_frontend_supported(uint32_t rows, uint32_t cols, uint32_t k);
+/* d_scratch of bsq_frontend_quantize.  Its fourth 32-bit word carries a selection bound from one call to the next
+ * on the same scratch area (a speed-up for runs of alike matrices; results never depend on it); zero the first 16
+ * bytes once after allocating it.  Calls that overlap on the GPU need scratch areas of their own. */
 size_t bsq_frontend_scratch_bytes(uint32_t rows, uint32_t cols);
 int bsq_frontend_quantize(int method, const float *d_in, uint32_t rows, uint32_t cols, uint32_t k, uint16_t *d_idx,
                           float *d_val, float *d_scales_f32, float *d_dq, uint8_t *d_scale_codes, uint8_t *d_data,

@@ -200,7 +200,8 @@ def test_topk_apply(lib, oracle):
     assert int(d_st[0]) != 0
 
 
-def frontend_gpu(lib, x, k, method):
+def frontend_gpu(lib, x, k, method, carried=None, calls=1):
+    """carried: bit pattern put into the scratch word that carries the selection bound from call to call."""
     rows, cols = x.shape
     n = rows * cols
     nb = n // 64
@@ -214,9 +215,12 @@ def frontend_gpu(lib, x, k, method):
     d_scr = torch.zeros(lib.bsq_frontend_scratch_bytes(rows, cols), dtype=torch.uint8, device="cuda")
     d_st = torch.zeros(4, dtype=torch.int32, device="cuda")
     assert lib.bsq_frontend_supported(rows, cols, k) == 1
-    rc = lib.bsq_frontend_quantize(method, d_x.data_ptr(), rows, cols, k, d_idx.data_ptr(), d_val.data_ptr(), d_s.data_ptr(),
-                                   d_dq.data_ptr(), d_c.data_ptr(), d_data.data_ptr(), d_scr.data_ptr(), d_st.data_ptr(), None)
-    assert rc == 0
+    if carried is not None:
+        d_scr.view(torch.int32)[3] = int(np.array([carried], dtype=np.uint32).view(np.int32)[0])
+    for _ in range(calls):
+        rc = lib.bsq_frontend_quantize(method, d_x.data_ptr(), rows, cols, k, d_idx.data_ptr(), d_val.data_ptr(), d_s.data_ptr(),
+                                       d_dq.data_ptr(), d_c.data_ptr(), d_data.data_ptr(), d_scr.data_ptr(), d_st.data_ptr(), None)
+        assert rc == 0
     torch.cuda.synchronize()
     assert int(d_st[0]) == 0
     return (d_idx.cpu().numpy().view(np.uint16), d_val.cpu().numpy(), d_s.cpu().numpy(), d_dq.cpu().numpy()[0],
@@ -241,6 +245,21 @@ def test_frontend_matches_oracle(lib, oracle, shape_k):
             dqo, co, do = oracle.nf4dq_quantize(zo)
             assert bits(np.array([dq]))[0] == bits(np.array([dqo]))[0]
             assert np.array_equal(c, co) and np.array_equal(data, do)
+
+
+@pytest.mark.parametrize("method", [10, 11])
+def test_frontend_result_does_not_depend_on_the_carried_bound(lib, method):
+    # whatever the scratch word holds (nothing, the bound of an earlier call on the same or on a differently scaled
+    # matrix, denormal, huge, infinite, NaN, negative), the bytes that come out are the same
+    rows, cols, k = 96, 4096, 41
+    x = make_c2_like(rows, cols, 77)
+    want = frontend_gpu(lib, x, k, method)
+    again = frontend_gpu(lib, x, k, method, calls=3)                 # the second and third call start from a carried bound
+    cases = [0x00000001, 0x00800000, 0x3A83126F, 0x3F800000, 0x41200000, 0x7F7FFFFF, 0x7F800000, 0x7FC00000, 0xBF800000, 0xFFFFFFFF]
+    outs = [again] + [frontend_gpu(lib, x, k, method, carried=c) for c in cases]
+    for got in outs:
+        for a, b in zip(want, got):
+            assert np.array_equal(bits(np.asarray(a)), bits(np.asarray(b))) if np.asarray(a).dtype == np.float32 else np.array_equal(a, b)
 
 
 def test_residual_error(lib, oracle):
