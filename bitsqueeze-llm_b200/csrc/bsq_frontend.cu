@@ -20,6 +20,8 @@
 #include "bsq_rowstream.cuh"
 
 #include <cstdlib>
+#include <mutex>
+#include <vector>
 
 namespace bsq {
 namespace {
@@ -38,16 +40,22 @@ __host__ __device__ inline StreamLayout stream_layout(unsigned cols, int code_bu
     return l;
 }
 
-// Row hand-out: lane 0 keeps the counter value it asked for one row ago (`pending`), publishes it and asks for
-// the next, so that the latency of the global atomic never shows; also clears the row flags.  Returns the
-// counter value (uniform; >= rows: no work left).
+// Row hand-out: a group's first row is its own number among the grid's groups (no atomic: all groups starting at once
+// on one counter would queue up for microseconds); further rows come from a global counter, offset by the number of
+// groups.  Lane 0 keeps the value it asked for one row ago (`pending`), publishes it and asks for the next, so that
+// the latency of the global atomic never shows; also clears the row flags.  Returns the row (uniform; >= rows: no
+// work left).
+template <int G>
+__device__ __forceinline__ unsigned first_row_of_group(const RowGroup<G> &g) {
+    return blockIdx.x * (blockDim.x / RowGroup<G>::L) + g.gid;
+}
 template <int G>
 __device__ __forceinline__ unsigned stream_next_row(const RowGroup<G> &g, GroupCtl &c, unsigned *row_counter, unsigned &pending,
                                                     unsigned rows) {
     if (g.lane == 0) {
         c.next_row = pending;
         c.flags = 0;
-        if (pending < rows) pending = atomicAdd(row_counter, 1u);
+        if (pending < rows) pending = gridDim.x * (blockDim.x / RowGroup<G>::L) + atomicAdd(row_counter, 1u);
     }
     g.sync();
     return c.next_row;
@@ -76,14 +84,16 @@ __global__ void __launch_bounds__(256, 4)
     unsigned *blk = reinterpret_cast<unsigned *>(base + lay.blk_off);
     unsigned *bitmap = reinterpret_cast<unsigned *>(base + lay.bitmap_off);
     const unsigned blocks_per_row = cols >> 6;
-    unsigned pending = 0;
-    if (g.lane == 0) pending = atomicAdd(row_counter, 1u);
+    unsigned pending = first_row_of_group<G>(g);
     float run = 0.0f, hint = k > 0 ? carried_hint(hint_word) : 0.0f;
+    bool fresh = false;                                      // the row before has left the control block clean
     for (;;) {
         const unsigned r = stream_next_row<G>(g, c, row_counter, pending, rows);
         if (r >= rows) break;
         hint = stream_select_absmax<G>(g, c, blk, bitmap, GlobalRow{in + (size_t)r * cols}, cols, k, out_idx + (size_t)r * k,
-                                       out_val + (size_t)r * k, hint, absmax_scratch + (size_t)r * blocks_per_row, &run);
+                                       out_val + (size_t)r * k, hint, absmax_scratch + (size_t)r * blocks_per_row, &run, fresh,
+                                       true, true);
+        fresh = true;
     }
     if (g.lane == 0 && hint > 0.0f) *hint_word = __float_as_uint(hint);      // whichever group writes last: all are usable
     run = warp_max(run);
@@ -125,8 +135,7 @@ __global__ void __launch_bounds__(256, 4)
     const float dq = dq_from_max(__uint_as_float(*gmax_bits));
     if (blockIdx.x == 0 && threadIdx.x == 0) *dq_out = dq;
     unsigned buf = 0;
-    unsigned pending = 0;
-    if (g.lane == 0) pending = atomicAdd(row_counter, 1u);
+    unsigned pending = first_row_of_group<G>(g);
     for (;;) {
         if (g.lane == 0) bulk_wait_read_1();                 // the store issued two rows ago has left its staging buffer
         const unsigned rr = stream_next_row<G>(g, c, row_counter, pending, rows);
@@ -167,8 +176,7 @@ __global__ void __launch_bounds__(256, 2)
     Nf4Lut lut;
     lut.load();
     unsigned buf = 0;
-    unsigned pending = 0;
-    if (g.lane == 0) pending = atomicAdd(row_counter, 1u);
+    unsigned pending = first_row_of_group<G>(g);
     float run = 0.0f, hint = k > 0 ? carried_hint(hint_word) : 0.0f;
     for (;;) {
         if (g.lane == 0) bulk_wait_read_1();
@@ -210,14 +218,42 @@ FrontGeometry front_geometry(uint32_t cols, int code_buffers) {
     return f;
 }
 
+// CTAs that fill the device for `kernel` with this much dynamic shared memory.  The attribute call and the occupancy
+// query cost microseconds of host time each, a tenth of what the stage itself takes, so their answer is kept per
+// (device, kernel, shared-memory size).
 template <typename K>
 cudaError_t persistent_grid(K kernel, int threads, size_t smem, int sm_count, unsigned rows, int groups, unsigned *grid_out) {
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    struct Known {
+        int device;
+        const void *kernel;
+        size_t smem;
+        int per_sm;
+    };
+    static std::mutex lock;
+    static std::vector<Known> known;
+    int device = 0, per_sm = 0;
+    cudaError_t err = cudaGetDevice(&device);
     if (err != cudaSuccess) return err;
-    int per_sm = 0;
-    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem);
-    if (err != cudaSuccess) return err;
-    if (per_sm < 1) per_sm = 1;
+    {
+        std::lock_guard<std::mutex> hold(lock);
+        for (const Known &e : known)
+            if (e.device == device && e.kernel == reinterpret_cast<const void *>(kernel) && e.smem == smem) per_sm = e.per_sm;
+    }
+    if (per_sm == 0) {
+        size_t largest = smem;                               // the attribute is only ever raised: sizes asked for earlier stay valid
+        {
+            std::lock_guard<std::mutex> hold(lock);
+            for (const Known &e : known)
+                if (e.device == device && e.kernel == reinterpret_cast<const void *>(kernel) && e.smem > largest) largest = e.smem;
+        }
+        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)largest);
+        if (err != cudaSuccess) return err;
+        err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem);
+        if (err != cudaSuccess) return err;
+        if (per_sm < 1) per_sm = 1;
+        std::lock_guard<std::mutex> hold(lock);
+        known.push_back({device, reinterpret_cast<const void *>(kernel), smem, per_sm});
+    }
     unsigned grid = (unsigned)sm_count * (unsigned)per_sm;
     const unsigned needed = (rows + groups - 1) / groups;
     *grid_out = grid > needed ? needed : grid;

@@ -285,14 +285,17 @@ __device__ __noinline__ void stream_exact(const RowGroup<G> &g, GroupCtl &c, uns
 //   bitmap : shared, cols / 32 words (exact path only)
 //   hint   : bound guess from the row before (0 = none);  returns the guess for the next row
 //   run    : running maximum of the block values of this lane
-//   fresh  : the caller has run stream_reset (and zeroed c.flags) before its last sync
+//   fresh  : stream_reset has run (and c.flags is zero) since the last use of the control block, with a sync behind it
+//   reset_after : run stream_reset for the next row before the final sync (whose caller then passes fresh = true):
+//            one group sync less per row
 //   sync_end = false leaves out the final sync (the caller's next sync then orders the blk[] reads)
 // The caller has zeroed c.flags and synchronised the group since; ends with a group sync.
 template <int G, class Row>
 __device__ __forceinline__ float stream_select_absmax(const RowGroup<G> &g, GroupCtl &c, unsigned *blk, unsigned *bitmap,
                                                       const Row &row, unsigned cols, unsigned k,
                                                       uint16_t *out_idx, float *out_val, float hint, float *absmax_out,
-                                                      float *run, bool fresh = false, bool sync_end = true) {
+                                                      float *run, bool fresh = false, bool sync_end = true,
+                                                      bool reset_after = false) {
     constexpr unsigned L = RowGroup<G>::L;
     const unsigned f4 = cols >> 2, nblk = cols >> 6;
     float next_hint = 0.0f;
@@ -342,6 +345,7 @@ __device__ __forceinline__ float stream_select_absmax(const RowGroup<G> &g, Grou
         reinterpret_cast<float *>(blk)[b] = fin;
         *run = fmaxf(*run, v);
     }
+    if (reset_after) stream_reset<G>(g, c);                  // nothing reads the candidate lists after the ranking's last sync
     if (sync_end) g.sync();
     return next_hint;
 }
