@@ -167,17 +167,19 @@ SVD_CONFIGS = {
     # name: outlier ratio, error ratio, rank, niters, U/V format, S format
     "C3": dict(outlier=0.0, error=0.0, rank=128, niters=2, uv=-1, s=-1),
     "C4": dict(outlier=0.005, error=0.01, rank=256, niters=2, uv=11, s=-1),
+    # one of the 32 independent 4096 x 14336 matrices of configs[4] (rows < columns: the SVD works on the transpose)
+    "C5a": dict(outlier=0.005, error=0.01, rank=256, niters=2, uv=11, s=-1),
 }
 
 
 def make_svd_matrix(name, torch):
-    m, n, r = 8192, 4096, 512
+    m, n, r = (4096, 14336, 512) if name == "C5a" else (8192, 4096, 512)
     g = torch.Generator(device="cuda").manual_seed(3)
     g1, _ = torch.linalg.qr(torch.randn(m, r, device="cuda", generator=g, dtype=torch.float64))
     g2, _ = torch.linalg.qr(torch.randn(n, r, device="cuda", generator=g, dtype=torch.float64))
     sv = torch.arange(1, r + 1, device="cuda", dtype=torch.float64) ** -1.0
     a = (g1 * sv) @ g2.T + 0.01 * torch.randn(m, n, device="cuda", generator=g, dtype=torch.float64)
-    if name == "C4":                                   # outlier channels and heavy-tailed entries on top
+    if name in ("C4", "C5a"):                          # outlier channels and heavy-tailed entries on top
         cols = torch.randperm(n, device="cuda", generator=g)[: max(1, round(0.0005 * n))]
         a[:, cols] *= 50.0
         mask = torch.rand(m, n, device="cuda", generator=g) < 0.01
@@ -266,7 +268,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--stage-only", action="store_true",
                     help="run only the device-stage loop (for profiler captures); prints no bench line")
-    ap.add_argument("--svd", default=None, choices=["C3", "C4"],
+    ap.add_argument("--svd", default=None, choices=["C3", "C4", "C5a"],
                     help="side measurement, not the bench line: time bitsqz_llm_compress / decompress of an SVD "
                          "configuration (device input); with --impl reference the reference's own CUDA build is timed")
     args = ap.parse_args()
