@@ -71,3 +71,18 @@ def test_gemm_tensor_core_path_is_repeatable(lib):
     first = run(lib, a, b, M, N, K, True, False, True, workspace)
     for _ in range(3):
         assert torch.equal(first, run(lib, a, b, M, N, K, True, False, True, workspace))
+
+
+def test_gemm_with_b_split_beforehand_for_every_shape():
+    """BSQ_GEMM_IMAGE=2 sends every product that can take it (also those of up to 128 columns, which by default
+    stay on the kernel that splits B in every CTA) to the kernel fed by bulk copies of pre-split images; the switch
+    is read once per process, so the accuracy test runs again in a child process."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, BSQ_GEMM_IMAGE="2")
+    here = os.path.dirname(os.path.abspath(__file__))
+    res = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_gpu_gemm.py"), "-q", "-x", "-m", "gpu",
+                          "-k", "test_gemm_matches_fp64 or test_gemm_tensor_core_path_is_repeatable"],
+                         env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
