@@ -74,6 +74,7 @@ SIGNATURES = {
     "bsq_nf4dq_quantize_static": (_i, [_vp, _u64, _vp, _vp, _vp, _vp]),
     "bsq_nf4_dequantize": (_i, [_vp, _vp, _u64, _vp, _vp]),
     "bsq_nf4dq_dequantize": (_i, [_vp, _vp, _vp, _u64, _vp, _vp]),
+    "bsq_dequantize_add_topk": (_i, [_i, _vp, _vp, _vp, _vp, _u32, _u32, _vp, _vp, _u32, _vp, _vp, _vp]),
     "bsq_frontend_supported": (_i, [_u32, _u32, _u32]),
     "bsq_frontend_scratch_bytes": (_sz, [_u32, _u32]),
     "bsq_frontend_quantize": (_i, [_i, _vp, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),

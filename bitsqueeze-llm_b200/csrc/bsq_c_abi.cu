@@ -83,6 +83,15 @@ int bsq_nf4dq_dequantize(const float *d_dq, const uint8_t *d_scale_codes, const 
     return rc(nf4dq_dequantize(d_dq, d_scale_codes, d_data, n, d_out, device_sm_count(), as_stream(stream)));
 }
 
+int bsq_dequantize_add_topk(int method, const float *d_scales_f32, const float *d_dq, const uint8_t *d_scale_codes,
+                            const uint8_t *d_data, uint32_t rows, uint32_t cols, const uint16_t *d_idx, const float *d_val,
+                            uint32_t k, float *d_out, uint32_t *d_status, void *stream) {
+    if (method != 10 && method != 11) return 1;
+    return rc(nf4_dequantize_add_topk(method == 11 ? d_scales_f32 : nullptr, method == 10 ? d_dq : nullptr,
+                                      method == 10 ? d_scale_codes : nullptr, d_data, rows, cols, d_idx, d_val, k, d_out, d_status,
+                                      device_sm_count(), as_stream(stream)));
+}
+
 int bsq_frontend_supported(uint32_t rows, uint32_t cols, uint32_t k) { return frontend_supported(rows, cols, k) ? 1 : 0; }
 size_t bsq_frontend_scratch_bytes(uint32_t rows, uint32_t cols) { return frontend_scratch_bytes(rows, cols); }
 int bsq_frontend_quantize(int method, const float *d_in, uint32_t rows, uint32_t cols, uint32_t k, uint16_t *d_idx,

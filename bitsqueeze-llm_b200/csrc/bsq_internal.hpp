@@ -25,6 +25,10 @@ cudaError_t nf4_dequantize(const float *d_scales, const uint8_t *d_data, uint64_
                            cudaStream_t stream);
 cudaError_t nf4dq_dequantize(const float *d_dq, const uint8_t *d_scale_codes, const uint8_t *d_data, uint64_t n,
                              float *d_out, int sm_count, cudaStream_t stream);
+// Dequantise a rows x cols matrix and add a row-wise top-k list in one pass; d_scales (NF4) or d_dq + d_scale_codes (NF4_DQ).
+cudaError_t nf4_dequantize_add_topk(const float *d_scales, const float *d_dq, const uint8_t *d_scale_codes, const uint8_t *d_data,
+                                    uint32_t rows, uint32_t cols, const uint16_t *d_idx, const float *d_val, uint32_t k,
+                                    float *d_out, unsigned *d_status, int sm_count, cudaStream_t stream);
 
 // ---- per-row top-k (bsq_topk.cu) ------------------------------------------------------------
 // k = (uint16)roundf(cols * ratio) clamped to cols, at least 1 for ratio > 0; -1 for a ratio

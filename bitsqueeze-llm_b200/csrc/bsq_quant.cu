@@ -196,11 +196,18 @@ __global__ void __launch_bounds__(kThreads)
 }
 
 // ---- decode ----------------------------------------------------------------------------------
+// Optional (idx non-null): a row-wise top-k list to add onto the decoded rows x cols matrix in the same pass.
+struct TopkList {
+    const uint16_t *idx;
+    const float *val;
+    unsigned cols, k;
+    unsigned *status;
+};
 template <bool DQ>
 __global__ void __launch_bounds__(kThreads)
     decode_flat_kernel(const float *__restrict__ scales_f32, const uint8_t *__restrict__ scale_codes,
                        const float *__restrict__ dq_in, const uint8_t *__restrict__ data, uint64_t n, bool vec,
-                       float *__restrict__ out) {
+                       float *out, TopkList add) {
     const int lane = threadIdx.x & 31;
     const uint64_t warp = (uint64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
     const uint64_t nwarps = (uint64_t)gridDim.x * (kThreads / 32);
@@ -250,6 +257,23 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll
                 for (int q = 0; q < 8; ++q)
                     if (e + q < n) out[e + q] = d[q];
+            }
+        }
+        if (add.idx) {
+            // dense[row, idx] += value (topk_cuda.cuh:83-86) for the entries that fall into the kBatch elements this
+            // warp has just written: the row(s) of the batch, k entries each, a few per lane
+            __syncwarp();                                     // the warp's stores are ordered before its reads below
+            const uint64_t last = (base + kBatch <= n ? base + kBatch : n) - 1;
+            for (uint64_t r = base / add.cols; r <= last / add.cols; ++r) {
+                for (unsigned j = lane; j < add.k; j += 32) {
+                    const unsigned c = add.idx[r * add.k + j];
+                    if (c < add.cols) {
+                        const uint64_t pos = r * add.cols + c;
+                        if (pos >= base && pos <= last) out[pos] = out[pos] + add.val[r * add.k + j];
+                    } else if (add.status) {
+                        atomicOr(add.status, kStatusBadIndex);
+                    }
+                }
             }
         }
     }
@@ -335,7 +359,7 @@ cudaError_t nf4_dequantize(const float *d_scales, const uint8_t *d_data, uint64_
                            cudaStream_t stream) {
     const bool vec = aligned(d_data, 4) && aligned(d_out, 16);
     decode_flat_kernel<false><<<grid_for(n, sm_count), kThreads, 0, stream>>>(d_scales, nullptr, nullptr, d_data, n, vec,
-                                                                                d_out);
+                                                                                d_out, TopkList{});
     return cudaGetLastError();
 }
 
@@ -343,7 +367,25 @@ cudaError_t nf4dq_dequantize(const float *d_dq, const uint8_t *d_scale_codes, co
                              float *d_out, int sm_count, cudaStream_t stream) {
     const bool vec = aligned(d_data, 4) && aligned(d_out, 16);
     decode_flat_kernel<true><<<grid_for(n, sm_count), kThreads, 0, stream>>>(nullptr, d_scale_codes, d_dq, d_data, n, vec,
-                                                                               d_out);
+                                                                               d_out, TopkList{});
+    return cudaGetLastError();
+}
+
+// Dequantise a rows x cols matrix and add its row-wise top-k list in the same pass (quantization_cuda_decompress
+// followed by topk_apply in the reference, src/bitsqz_llm.cu:1304-1393).  d_scales: FP32 block scales (NF4) or null;
+// d_dq + d_scale_codes: NF4_DQ or null.
+cudaError_t nf4_dequantize_add_topk(const float *d_scales, const float *d_dq, const uint8_t *d_scale_codes, const uint8_t *d_data,
+                                    uint32_t rows, uint32_t cols, const uint16_t *d_idx, const float *d_val, uint32_t k,
+                                    float *d_out, unsigned *d_status, int sm_count, cudaStream_t stream) {
+    if (!d_data || !d_out || !d_idx || !d_val || rows == 0 || cols == 0 || k == 0) return cudaErrorInvalidValue;
+    if ((d_scales != nullptr) == (d_dq != nullptr && d_scale_codes != nullptr)) return cudaErrorInvalidValue;
+    const uint64_t n = (uint64_t)rows * cols;
+    const bool vec = aligned(d_data, 4) && aligned(d_out, 16);
+    const TopkList add{d_idx, d_val, cols, k, d_status};
+    if (d_scales)
+        decode_flat_kernel<false><<<grid_for(n, sm_count), kThreads, 0, stream>>>(d_scales, nullptr, nullptr, d_data, n, vec, d_out, add);
+    else
+        decode_flat_kernel<true><<<grid_for(n, sm_count), kThreads, 0, stream>>>(nullptr, d_scale_codes, d_dq, d_data, n, vec, d_out, add);
     return cudaGetLastError();
 }
 

@@ -91,6 +91,13 @@ int bsq_nf4dq_quantize_static(const float *d_x, uint64_t n, float *d_dq, uint8_t
 int bsq_nf4_dequantize(const float *d_scales, const uint8_t *d_data, uint64_t n, float *d_out, void *stream);
 int bsq_nf4dq_dequantize(const float *d_dq, const uint8_t *d_scale_codes, const uint8_t *d_data, uint64_t n,
                          float *d_out, void *stream);
+/* quantization_cuda_decompress followed by topk_apply on the same rows x cols matrix (the no-SVD branch of
+ * bitsqz_llm_decompress, src/bitsqz_llm.cu:1304-1393) in one pass over the output: d_out = dequantise(...) and then
+ * d_out[row, idx] += val for the row's k entries.  method 11: d_scales_f32; method 10: d_dq and d_scale_codes.
+ * Columns out of range are skipped and reported in d_status (bit 1), as by bsq_topk_apply. */
+int bsq_dequantize_add_topk(int method, const float *d_scales_f32, const float *d_dq, const uint8_t *d_scale_codes,
+                            const uint8_t *d_data, uint32_t rows, uint32_t cols, const uint16_t *d_idx, const float *d_val,
+                            uint32_t k, float *d_out, uint32_t *d_status, void *stream);
 
 /* ---- fused outlier separation + quantiser: the no-SVD branch of bitsqz_llm_compress
  * (src/bitsqz_llm.cu:1045-1056,1183-1195) as one stage --------------------------------------- */

@@ -262,6 +262,42 @@ def test_frontend_result_does_not_depend_on_the_carried_bound(lib, method):
             assert np.array_equal(bits(np.asarray(a)), bits(np.asarray(b))) if np.asarray(a).dtype == np.float32 else np.array_equal(a, b)
 
 
+@pytest.mark.parametrize("shape_k", [(64, 4096, 41), (37, 192, 5), (300, 64, 1), (5, 14336, 143), (129, 1024, 10)])
+@pytest.mark.parametrize("method", [10, 11])
+def test_dequantize_add_topk_equals_the_two_stages(lib, shape_k, method):
+    # one pass (decode, then the row's k entries added) against bsq_nf4*_dequantize followed by bsq_topk_apply: same bits;
+    # rows shorter and longer than a warp's batch of 1024 elements, batches that straddle rows, a ragged last batch
+    rows, cols, k = shape_k
+    x = make_c2_like(rows, cols, rows * 7 + cols)
+    idx, val, s, dq, c, data = frontend_gpu(lib, x, k, method)
+    n = rows * cols
+    d_idx, d_val = dev(idx.view(np.int16)), dev(val)
+    d_s, d_dq, d_c, d_data = dev(s), dev(np.array([dq, 0, 0, 0], np.float32)), dev(c), dev(data)
+    want = torch.full((rows, cols), 7.0, dtype=torch.float32, device="cuda")
+    got = torch.full((rows, cols), 9.0, dtype=torch.float32, device="cuda")
+    d_st = torch.zeros(4, dtype=torch.int32, device="cuda")
+    if method == 11:
+        assert lib.bsq_nf4_dequantize(d_s.data_ptr(), d_data.data_ptr(), n, want.data_ptr(), None) == 0
+    else:
+        assert lib.bsq_nf4dq_dequantize(d_dq.data_ptr(), d_c.data_ptr(), d_data.data_ptr(), n, want.data_ptr(), None) == 0
+    assert lib.bsq_topk_apply(d_idx.data_ptr(), d_val.data_ptr(), rows, cols, k, want.data_ptr(), d_st.data_ptr(), None) == 0
+    assert lib.bsq_dequantize_add_topk(method, d_s.data_ptr(), d_dq.data_ptr(), d_c.data_ptr(), d_data.data_ptr(), rows, cols,
+                                       d_idx.data_ptr(), d_val.data_ptr(), k, got.data_ptr(), d_st.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    assert int(d_st[0]) == 0
+    assert torch.equal(want.view(torch.int32), got.view(torch.int32))
+    # and it gives the input back where the input was an outlier
+    r0 = got.cpu().numpy()
+    assert np.array_equal(bits(r0[np.arange(rows)[:, None], idx.astype(np.int64)]), bits(val))
+    # a column out of range is skipped and reported
+    bad = idx.copy()
+    bad[0, 0] = 65000
+    assert lib.bsq_dequantize_add_topk(method, d_s.data_ptr(), d_dq.data_ptr(), d_c.data_ptr(), d_data.data_ptr(), rows, cols,
+                                       dev(bad.view(np.int16)).data_ptr(), d_val.data_ptr(), k, got.data_ptr(), d_st.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    assert int(d_st[0]) != 0
+
+
 def test_residual_error(lib, oracle):
     rng = np.random.default_rng(41)
     for n in (5, 64, 1000, 4099):
