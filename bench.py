@@ -1,33 +1,37 @@
 """Benchmark of the bitsqz_llm compress/decompress hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--lanes L]
 
-Workload (BASELINE.json configs[1]): one 4096 x 4096 FP32 activation matrix per step -- N(0,1) with
-0.1 % of the columns scaled by U[20,100] -- outlier top-k ratio 0.01, NF4_DQ, no SVD.  Data is
-seeded synthetic.  A step is one pass of the hot path (per-row outlier separation fused with the
-NF4_DQ quantiser) over one matrix.
+Workload (the largest configuration of the path, BASELINE.json configs[4]): a batch of 32 independent FP32 activation
+matrices of 4096 x 14336 (per-layer seeds, seeded synthetic: low-rank + noise + outlier channels + heavy-tailed
+entries, bitsqueeze-llm_b200/workloads.py), full pipeline: outlier top-k 0.005, randomized SVD rank 256 with 2 power
+iterations, U/V in NF4, S in FP32, error-correction top-k 0.01; compress AND decompress.  Matrix i belongs to rank
+i % N (one process per GPU, no collective on the data path: the matrices are independent, weak-free strong split of a
+fixed batch).  A step is one pass over the rank's share of the batch: every matrix compressed, then every object
+decompressed.  Inputs (235 MB each) are larger than the L2.
 
-  value  FP32-input GB/s of the device stages with the input resident in HBM (CUDA events, barrier +
-         synchronize on both sides, max over ranks).  Matrices are independent, so the job keeps two of
-         them in flight on two streams; the single-stream time per step is reported in config.  Successive
-         steps rotate over 4 different input matrices (256 MiB > the 126 MB L2), so no step finds its
-         input in L2 from the step before.
-  e2e    the same metric through the public bitsqz_llm_compress call with a pinned HOST matrix:
-         host->device copy of the input and device->host copy of the packed object inside the
-         timed region.
-  roofline      dominant kernel (frontend_select_kernel: row sweep, top-k selection, block maxima) from
-                per-kernel CUDA events; algorithmic bytes per launch / duration against the measured HBM peak.
-  cpu_baseline  rank 0, N=1: the same workload on the host cores -- reference CPU NF4_DQ quantiser
-                (oracle/_ref, built from the reference's own sources) behind the oracle's top-k port
-                (the reference has no CPU top-k).
+  value   FP32 bytes of the whole batch / time of a step, inputs resident in HBM, packed objects left in device
+          memory (device-resident objects through the batch entry points, `lanes` matrices in flight per GPU); CUDA
+          events, barrier + synchronize on both sides, max over ranks.  compress / decompress are reported separately
+          beside it, and the same with one matrix at a time (lanes = 1).
+  e2e     the same step with HOST buffers: matrices in pinned host memory, packed objects returned as host objects
+          (the public object format), decompress from those host objects; host<->device copies inside the timed region.
+  roofline      the tcgen05 3xTF32 product kernel (gemm_tc_image_kernel: the six products of the range finder with the
+                4096 x 14336 matrix), timed by CUDA events on its stream in a one-lane pass; FLOPs 2 M N K per launch
+                against the TF32 dense rate measured in this run / 3.
+  cpu_baseline  rank 0, N=1: the only stage of this pipeline the reference can run on a CPU -- its OpenMP NF4 quantiser
+                (oracle/_ref/libref_cpu.so) on arrays of U's and V's size -- on all host cores.
 
-With --impl reference the CPU pipeline above is what gets timed (the reference's GPU build is a parity
-oracle in tests, not a bench arm).  Multi-GPU: one process per GPU under torchrun, independent matrices
-per rank, no collective on the data path (weak scaling).
+--impl reference times the reference's own CUDA build (oracle/_ref/libref_cuda.so, its five .cu files compiled
+unmodified for sm_100) on the same batch through its public calls, on rank 0's GPU (the reference has no multi-GPU
+mode and no CPU path for top-k, SVD or reconstruction).
+--single C3|C4|C5A times the public compress / decompress calls on one matrix of that configuration (a side
+measurement for profiles; with --impl reference through the reference's CUDA build).
 """
 import argparse
 import ctypes as C
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -40,30 +44,41 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 import __graft_entry__ as entry  # noqa: E402
 
-ROWS, COLS, OUTLIER_RATIO, METHOD = 4096, 4096, 0.01, 10
-NBUF = 4
-INFLIGHT = 2            # matrices in flight in the device-stage loop, one stream each
-# dram__bytes_read.sum + dram__bytes_write.sum of one frontend_select_kernel launch on this workload, from the ncu
-# capture summarised in profiles/frontend_nf4dq_c2_4096x4096.md (67 174 400 + 502 272)
-NCU_TRAFFIC_SELECT = 67676672
-METRIC = "FP32-input GB/s, compress (outlier top-k 0.01 + NF4_DQ) of a 4096x4096 FP32 matrix"
+METRIC = "FP32-input GB/s, compress+decompress of 32 x (4096x14336) FP32 matrices, full pipeline"
+WORKLOAD = ("configs[4]: 32 independent 4096x14336 FP32 matrices, outlier_topk=0.005, SVD rank 256 (2 power iterations), "
+            "U/V NF4, S FP32, error_correction_topk=0.01, compress+decompress, matrix i on rank i % N")
+# kernels this library launches per matrix in this configuration (ncu launch list of `--single C5A`; the figure is
+# stated next to the list in profiles/)
+LAUNCHES_PER_COMPRESS = 96
+LAUNCHES_PER_DECOMPRESS = 7
 
 
-def make_matrix(seed):
-    rng = np.random.default_rng(seed)
-    x = rng.standard_normal((ROWS, COLS), dtype=np.float32)
-    ncol = max(1, int(round(0.001 * COLS)))
-    for c in rng.choice(COLS, size=ncol, replace=False):
-        x[:, c] *= np.float32(rng.uniform(20.0, 100.0))
-    return x
+def workloads():
+    import importlib
+    entry.load_package()
+    return importlib.import_module(entry.PKG_NAME + ".workloads")
+
+
+def load_shard():
+    import importlib
+    entry.load_package()
+    return importlib.import_module(entry.PKG_NAME + ".shard")
 
 
 def measured_peaks():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
     except Exception:
-        return 6650.0, "fallback"
+        return 6650.0, 1590.0, "fallback"
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
 class ClockSampler:
@@ -94,7 +109,7 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, smax, reasons = [], [], set()
+        sm, smax, power, reasons = [], [], [], set()
         for line in out.splitlines():
             f = [t.strip() for t in line.split(",")]
             if len(f) < 9:
@@ -102,6 +117,7 @@ class ClockSampler:
             try:
                 sm.append(float(f[1]))
                 smax.append(float(f[2]))
+                power.append(float(f[3]))
             except ValueError:
                 continue
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
@@ -109,98 +125,130 @@ class ClockSampler:
                     reasons.add(name)
         busy = [v for v in sm if v >= 0.5 * max(sm)] if sm else []
         return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_pipeline(orc_mod):
-    """(callable, kind, cores, description): outlier separation + NF4_DQ of one matrix on the host cores."""
-    oracle = orc_mod.Oracle()
+def rel_frob(x, y):
+    return float((x.double() - y.double()).norm() / x.double().norm())
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# the reference arm
+# ----------------------------------------------------------------------------------------------------------------
+def cpu_nf4_baseline(W, budget_s=12.0):
+    """The reference's OpenMP NF4 quantiser on arrays of the size of U and V of one matrix, all host threads."""
+    orc = entry.load_oracle()
     try:
-        ref = orc_mod.RefCpu()
+        q = orc.RefCpu()
+        kind = "reference"
     except (FileNotFoundError, OSError):
-        ref = None
-    k = oracle.topk_num_columns(COLS, OUTLIER_RATIO)
-
-    def step(x):
-        _, _, z = oracle.topk_rows(x, k, zero_selected=True)
-        if ref is not None:
-            ref.nf4dq_quantize(z)
-        else:
-            oracle.nf4dq_quantize(z)
-
-    cores = ref.max_threads() if ref is not None else oracle.max_threads()
-    kind = "reference" if ref is not None else "port"
-    desc = ("NF4_DQ: reference legacy CPU quantiser (OpenMP); top-k: oracle port, the reference has none on CPU"
-            if ref is not None else "oracle port (OpenMP) of top-k separation + NF4_DQ")
-    return step, kind, cores, desc
+        q = orc.Oracle()
+        kind = "port"
+    threads = host_threads()
+    q.set_threads(threads)                   # a launcher may have exported OMP_NUM_THREADS=1
+    cfg = W.CONFIGS["C5A"]
+    rng = np.random.default_rng(5)
+    u = rng.standard_normal(cfg["rows"] * cfg["rank"]).astype(np.float32) / 64
+    v = rng.standard_normal(cfg["cols"] * cfg["rank"]).astype(np.float32) / 64
+    q.nf4_quantize(u)
+    reps, t0 = 0, time.perf_counter()
+    while reps < 3 or (time.perf_counter() - t0 < budget_s and reps < 2000):
+        q.nf4_quantize(u)
+        q.nf4_quantize(v)
+        reps += 1
+    dt = time.perf_counter() - t0
+    return {"value": (u.size + v.size) * 4 * reps / dt / 1e9, "unit": "GB/s (FP32 input of the NF4 stage)", "cores": q.max_threads(),
+            "kind": kind,
+            "sample": "%d x NF4 of U (%d) and V (%d floats) of one matrix in %.1f s: the reference's legacy OpenMP quantiser, "
+                      "the one stage of this pipeline with a CPU path" % (reps, u.size, v.size, dt)}
 
 
 def run_reference(args, rank):
-    """--impl reference: the CPU implementation of the path on this box's host cores."""
+    """--impl reference: the reference's own CUDA build on the same batch, rank 0 only."""
     if rank != 0:
         return
-    orc = entry.load_oracle()
-    step, kind, cores, desc = cpu_pipeline(orc)
-    xs = [make_matrix(100 + i) for i in range(2)]
-    for i in range(max(1, min(args.warmup, 2))):
-        step(xs[i % 2])
+    W = workloads()
+    base = {"impl": "reference", "metric": METRIC, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": WORKLOAD}}
+    try:
+        ref = entry.load_oracle().RefCuda()
+    except (FileNotFoundError, OSError) as e:
+        print(json.dumps(dict(base, unavailable="oracle/_ref/libref_cuda.so (the reference's CUDA build) is not there: %s" % e)))
+        return
+    import torch
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    cfg = W.CONFIGS["C5A"]
+    rows, cols, n = cfg["rows"], cfg["cols"], cfg["rows"] * cfg["cols"]
+    mats = [W.config_matrix(torch, "C5A", layer=l) for l in range(W.C5A_LAYERS)]
+    L = ref.lib
+    assert L.ref_compress_initialize(rows, cols, cfg["outlier"], cfg["error"], cfg["rank"], cfg["niters"], cfg["uv"], cfg["s"], cfg["q"], 1) == 0
+    assert L.ref_decompress_initialize(rows, cols, cfg["outlier"], cfg["error"], cfg["rank"], cfg["uv"], cfg["s"], cfg["q"]) == 0
+    d_y = torch.zeros((rows, cols), dtype=torch.float32, device="cuda")
+    t_c = t_d = 0.0
+
+    def step(timed):
+        nonlocal t_c, t_d
+        objs = []
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for m in mats:
+            o = C.c_void_p(None)
+            if L.ref_compress(m.data_ptr(), C.byref(o), None) != 0:
+                raise RuntimeError("reference compress failed")
+            objs.append(o)
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        for o in objs:
+            if L.ref_decompress(o, d_y.data_ptr(), n) != 0:
+                raise RuntimeError("reference decompress failed")
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        for o in objs:
+            L.ref_free(o)
+        if timed:
+            t_c += t1 - t0
+            t_d += t2 - t1
+
+    warm = max(1, min(args.warmup, 3))
+    for _ in range(warm):
+        step(False)
+    err = rel_frob(mats[-1], d_y)
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
     t0 = time.perf_counter()
-    for i in range(args.steps):
-        step(xs[i % 2])
+    for _ in range(args.steps):
+        step(True)
     dt = time.perf_counter() - t0
-    gbs = ROWS * COLS * 4 * args.steps / dt / 1e9
-    line = {
-        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "configs[1]: 4096x4096 FP32, outlier_topk=0.01, NF4_DQ, no SVD", "rows": ROWS, "cols": COLS},
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind,
-                         "sample": f"{args.steps} full matrices per run; {desc}"},
-        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
-    }
+    clocks = sampler.stop()
+    L.ref_compress_release()
+    L.ref_decompress_release()
+    total_bytes = len(mats) * n * 4
+    gbs = total_bytes * args.steps / dt / 1e9
+    cpu = cpu_nf4_baseline(W)
+    line = dict(base, value=gbs, ms_per_step=dt / args.steps * 1e3,
+                compress={"value": total_bytes * args.steps / t_c / 1e9, "unit": "GB/s", "ms_per_matrix": t_c / args.steps / len(mats) * 1e3},
+                decompress={"value": total_bytes * args.steps / t_d / 1e9, "unit": "GB/s (FP32 output)", "ms_per_matrix": t_d / args.steps / len(mats) * 1e3},
+                rel_frob_last_layer=err, cpu_baseline=cpu,
+                reference_kind="the reference's CUDA build (oracle/_ref/libref_cuda.so) on one B200, device input, its public "
+                               "compress / decompress calls, all 32 matrices on rank 0's GPU; wall clock with a device "
+                               "synchronise on both sides",
+                e2e={"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                gpu_launches=0, clocks=clocks)
     print(json.dumps(line))
 
 
-# BASELINE.json configs[2] and configs[3]: 8192 x 4096, seeded synthetic.
-SVD_CONFIGS = {
-    # name: outlier ratio, error ratio, rank, niters, U/V format, S format
-    "C3": dict(outlier=0.0, error=0.0, rank=128, niters=2, uv=-1, s=-1),
-    "C4": dict(outlier=0.005, error=0.01, rank=256, niters=2, uv=11, s=-1),
-    # one of the 32 independent 4096 x 14336 matrices of configs[4] (rows < columns: the SVD works on the transpose)
-    "C5a": dict(outlier=0.005, error=0.01, rank=256, niters=2, uv=11, s=-1),
-}
-
-
-def make_svd_matrix(name, torch):
-    m, n, r = (4096, 14336, 512) if name == "C5a" else (8192, 4096, 512)
-    g = torch.Generator(device="cuda").manual_seed(3)
-    g1, _ = torch.linalg.qr(torch.randn(m, r, device="cuda", generator=g, dtype=torch.float64))
-    g2, _ = torch.linalg.qr(torch.randn(n, r, device="cuda", generator=g, dtype=torch.float64))
-    sv = torch.arange(1, r + 1, device="cuda", dtype=torch.float64) ** -1.0
-    a = (g1 * sv) @ g2.T + 0.01 * torch.randn(m, n, device="cuda", generator=g, dtype=torch.float64)
-    if name in ("C4", "C5a"):                          # outlier channels and heavy-tailed entries on top
-        cols = torch.randperm(n, device="cuda", generator=g)[: max(1, round(0.0005 * n))]
-        a[:, cols] *= 50.0
-        mask = torch.rand(m, n, device="cuda", generator=g) < 0.01
-        z = torch.randn(m, n, device="cuda", generator=g, dtype=torch.float64)
-        chi = (torch.randn(3, m, n, device="cuda", generator=g, dtype=torch.float64) ** 2).sum(0) / 3.0
-        a = torch.where(mask, a + 0.01 * z / chi.sqrt(), a)
-    return a.float().contiguous()
-
-
-def run_svd_config(args):
-    """Side measurement (not the bench line): bitsqz_llm_compress / decompress of an SVD configuration with a device
-    input.  --impl ours times this library; --impl reference times the reference's own CUDA build from oracle/_ref
-    (these stages have no CPU path in the reference)."""
+# ----------------------------------------------------------------------------------------------------------------
+# side measurement: one matrix through the public calls
+# ----------------------------------------------------------------------------------------------------------------
+def run_single(args):
     import torch
-    cfg = SVD_CONFIGS[args.svd]
-    a = make_svd_matrix(args.svd, torch)
+    W = workloads()
+    name = args.single.upper()
+    cfg = W.CONFIGS[name]
+    a = W.config_matrix(torch, name, layer=0)
     m, n = a.shape
     steps, warm = max(3, min(args.steps, 20)), max(2, min(args.warmup, 5))
-
-    def rel_frob(x, y):
-        return float((x.double() - y.double()).norm() / x.double().norm())
 
     def timed(fn):
         for _ in range(warm):
@@ -214,66 +262,166 @@ def run_svd_config(args):
             ts.append((time.perf_counter() - t0) * 1e3)
         return statistics.median(ts)
 
-    out = {"svd_config": args.svd, "impl": args.impl, "shape": [m, n], "steps": steps}
+    out = {"single": name, "impl": args.impl, "shape": [m, n], "steps": steps}
     y = torch.zeros_like(a)
+    ci = (m, n, cfg["outlier"], cfg["error"], cfg["rank"], cfg["niters"], cfg["uv"], cfg["s"], cfg["q"], 1)
+    di = (m, n, cfg["outlier"], cfg["error"], cfg["rank"], cfg["uv"], cfg["s"], cfg["q"])
     if args.impl == "ours":
         pkg = entry.load_package()
         L = pkg.lib()
-        assert L.bsq_compress_initialize(m, n, cfg["outlier"], cfg["error"], cfg["rank"], cfg["niters"], cfg["uv"], cfg["s"], -1, 1) == 0
-        assert L.bsq_decompress_initialize(m, n, cfg["outlier"], cfg["error"], cfg["rank"], cfg["uv"], cfg["s"], -1) == 0
-        blob = pkg.compress_to_bytes(a.data_ptr())[1]
+        assert L.bsq_compress_initialize(*ci) == 0 and L.bsq_decompress_initialize(*di) == 0
+        obj = C.c_void_p(None)
+        assert L.bsq_compress(a.data_ptr(), C.byref(obj), None) == 0
+        out["bytes"] = int(L.bsq_get_packed_size(obj))
 
-        def compress_call():                            # the public call and its free, nothing else
-            obj = C.c_void_p(None)
-            assert L.bsq_compress(a.data_ptr(), C.byref(obj), None) == 0
-            L.bsq_free(obj)
+        def compress_call():
+            o = C.c_void_p(None)
+            assert L.bsq_compress(a.data_ptr(), C.byref(o), None) == 0
+            L.bsq_free(o)
         out["compress_ms"] = timed(compress_call)
-        out["decompress_ms"] = timed(lambda: pkg.decompress_packed(blob, y.data_ptr(), m * n))
+        out["decompress_ms"] = timed(lambda: L.bsq_decompress(obj, y.data_ptr(), m * n))
+        prof = pkg.Profile()
+        o = C.c_void_p(None)
+        assert L.bsq_compress(a.data_ptr(), C.byref(o), C.byref(prof)) == 0
+        L.bsq_free(o)
+        out["profile_ms"] = {k: round(getattr(prof, k), 4) for k, _ in prof._fields_}
+        L.bsq_free(obj)
         L.bsq_compress_release()
         L.bsq_decompress_release()
     else:
         try:
             ref = entry.load_oracle().RefCuda()
         except (FileNotFoundError, OSError) as e:
-            print(json.dumps({"svd_config": args.svd, "impl": "reference", "unavailable": "oracle/_ref/libref_cuda.so not built: %s" % e}))
+            print(json.dumps({"single": name, "impl": "reference", "unavailable": "oracle/_ref/libref_cuda.so not built: %s" % e}))
             return
-        assert ref.lib.ref_compress_initialize(m, n, cfg["outlier"], cfg["error"], cfg["rank"], cfg["niters"], cfg["uv"], cfg["s"], -1, 1) == 0
-        assert ref.lib.ref_decompress_initialize(m, n, cfg["outlier"], cfg["error"], cfg["rank"], cfg["uv"], cfg["s"], -1) == 0
-        blob = ref.compress_bytes(a.data_ptr())
+        R = ref.lib
+        assert R.ref_compress_initialize(*ci) == 0 and R.ref_decompress_initialize(*di) == 0
+        obj = C.c_void_p(None)
+        assert R.ref_compress(a.data_ptr(), C.byref(obj), None) == 0
+        out["bytes"] = int(R.ref_get_packed_size(obj))
 
-        def rdec():
-            h = ref.lib.ref_load_from_buffer(blob.ctypes.data, blob.size)
-            rc = ref.lib.ref_decompress(h, y.data_ptr(), m * n)
-            ref.lib.ref_free(h)
-            assert rc == 0
         def compress_call():
-            obj = C.c_void_p(None)
-            assert ref.lib.ref_compress(a.data_ptr(), C.byref(obj), None) == 0
-            ref.lib.ref_free(obj)
+            o = C.c_void_p(None)
+            assert R.ref_compress(a.data_ptr(), C.byref(o), None) == 0
+            R.ref_free(o)
         out["compress_ms"] = timed(compress_call)
-        out["decompress_ms"] = timed(rdec)
-        ref.lib.ref_compress_release()
-        ref.lib.ref_decompress_release()
+        out["decompress_ms"] = timed(lambda: R.ref_decompress(obj, y.data_ptr(), m * n))
+        R.ref_free(obj)
+        R.ref_compress_release()
+        R.ref_decompress_release()
     out["rel_frob"] = rel_frob(a, y)
-    out["bytes"] = int(blob.size)
     out["fp32_input_gbs_compress"] = m * n * 4 / (out["compress_ms"] * 1e-3) / 1e9
     print(json.dumps(out))
 
 
+# ----------------------------------------------------------------------------------------------------------------
+# extra legs of the main line
+# ----------------------------------------------------------------------------------------------------------------
+def c2_frontend_leg(torch, pkg, L, W, hbm_peak):
+    """Configuration 2 (4096x4096, outlier 0.01 + NF4_DQ): the fused front end's two kernels and the decompress kernel,
+    device resident, CUDA events; inputs rotate over 4 matrices (256 MiB > L2)."""
+    rows = cols = 4096
+    n, nb = rows * cols, rows * cols // 64
+    k = L.bsq_topk_num_columns(cols, 0.01)
+    d_in = [torch.from_numpy(W.c2_matrix(seed=100 + i)).cuda() for i in range(4)]
+    idx = torch.zeros((rows, k), dtype=torch.int16, device="cuda")
+    val = torch.zeros((rows, k), dtype=torch.float32, device="cuda")
+    dq = torch.zeros(4, dtype=torch.float32, device="cuda")
+    codes = torch.zeros(nb, dtype=torch.uint8, device="cuda")
+    data = torch.zeros(n // 2, dtype=torch.uint8, device="cuda")
+    scr = torch.zeros(L.bsq_frontend_scratch_bytes(rows, cols), dtype=torch.uint8, device="cuda")
+    st = torch.zeros(4, dtype=torch.int32, device="cuda")
+    outs = [torch.zeros((rows, cols), dtype=torch.float32, device="cuda") for _ in range(4)]
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def stage(i):
+        if L.bsq_frontend_quantize(10, d_in[i % 4].data_ptr(), rows, cols, k, idx.data_ptr(), val.data_ptr(), None, dq.data_ptr(),
+                                   codes.data_ptr(), data.data_ptr(), scr.data_ptr(), st.data_ptr(), stream) != 0:
+            raise RuntimeError("bsq_frontend_quantize failed")
+
+    def dstage(i):
+        if L.bsq_dequantize_add_topk(10, None, dq.data_ptr(), codes.data_ptr(), data.data_ptr(), rows, cols, idx.data_ptr(),
+                                     val.data_ptr(), k, outs[i % 4].data_ptr(), st.data_ptr(), stream) != 0:
+            raise RuntimeError("bsq_dequantize_add_topk failed")
+
+    def loop(fn, reps):
+        for i in range(10):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+    ms_c = loop(stage, 400)
+    ms_d = loop(dstage, 400)
+    if int(st[0]) != 0:
+        raise RuntimeError("kernel status word set: %d" % int(st[0]))
+    ms_pass = (C.c_float * 2)()
+    p1, p2 = [], []
+    for i in range(16):
+        for j in range(3):
+            stage(i + j + 1)
+        if L.bsq_frontend_quantize_timed(10, d_in[i % 4].data_ptr(), rows, cols, k, idx.data_ptr(), val.data_ptr(), None,
+                                         dq.data_ptr(), codes.data_ptr(), data.data_ptr(), scr.data_ptr(), st.data_ptr(), stream,
+                                         ms_pass) != 0:
+            raise RuntimeError("bsq_frontend_quantize_timed failed")
+        p1.append(ms_pass[0])
+        p2.append(ms_pass[1])
+    bytes_stage = n * 4 + rows * k * 6 + n // 2 + nb + 4
+    bytes_p1 = n * 4 + rows * k * 6 + nb * 4
+    ach = bytes_stage / (ms_c * 1e-3) / 1e9
+    ach_d = bytes_stage / (ms_d * 1e-3) / 1e9
+    return {"workload": "configs[1]: " + W.describe("C2") + ", device resident, one stream",
+            "compress": {"fp32_input_gbs": n * 4 / (ms_c * 1e-3) / 1e9, "ms": ms_c, "hbm_gbs": ach, "frac_of_hbm_peak": ach / hbm_peak,
+                         "select_kernel_ms": statistics.mean(p1), "encode_kernel_ms": statistics.mean(p2),
+                         "select_kernel_frac": bytes_p1 / (statistics.mean(p1) * 1e-3) / 1e9 / hbm_peak},
+            "decompress": {"fp32_output_gbs": n * 4 / (ms_d * 1e-3) / 1e9, "ms": ms_d, "hbm_gbs": ach_d,
+                           "frac_of_hbm_peak": ach_d / hbm_peak, "kernel": "dequantise + outlier add in one kernel"}}
+
+
+def tf32_peak(torch):
+    """Dense TF32 rate of a library matrix product, the denominator of the 3xTF32 roofline: FP32 matmul 8192^3 with TF32
+    allowed, best of 10 (a measurement of the device, not part of the path)."""
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a = torch.randn(8192, 8192, device="cuda")
+        b = torch.randn(8192, 8192, device="cuda")
+        for _ in range(3):
+            torch.matmul(a, b)
+        best = 1e9
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch.matmul(a, b)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        return 2 * 8192 ** 3 / (best * 1e-3) / 1e12
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# the bench line
+# ----------------------------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--stage-only", action="store_true",
-                    help="run only the device-stage loop (for profiler captures); prints no bench line")
-    ap.add_argument("--svd", default=None, choices=["C3", "C4", "C5a"],
-                    help="side measurement, not the bench line: time bitsqz_llm_compress / decompress of an SVD "
-                         "configuration (device input); with --impl reference the reference's own CUDA build is timed")
+    ap.add_argument("--lanes", type=int, default=4, help="matrices in flight per GPU")
+    ap.add_argument("--layers", type=int, default=None, help="batch size (default: the configuration's 32)")
+    ap.add_argument("--single", default=None, choices=["C3", "C4", "C5A", "c3", "c4", "c5a"],
+                    help="side measurement, not the bench line: public compress / decompress of one matrix")
+    ap.add_argument("--skip-extras", action="store_true", help="leave out the configs[1] leg and the CPU baseline")
     args = ap.parse_args()
-    if args.svd:
-        run_svd_config(args)
+    if args.single:
+        run_single(args)
         return
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -288,6 +436,8 @@ def main():
 
     pkg = entry.load_package()
     L = pkg.lib()
+    W = workloads()
+    shard = load_shard()
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -297,192 +447,186 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    n = ROWS * COLS
-    k = L.bsq_topk_num_columns(COLS, OUTLIER_RATIO)
-    nb = n // 64
-    host = [make_matrix(1000 * rank + i) for i in range(NBUF)]
-    d_in = [torch.from_numpy(h).cuda() for h in host]
-
-    class Outputs:
-        """Device outputs and scratch of one matrix in flight."""
-        def __init__(self):
-            self.idx = torch.zeros((ROWS, k), dtype=torch.int16, device="cuda")
-            self.val = torch.zeros((ROWS, k), dtype=torch.float32, device="cuda")
-            self.dq = torch.zeros(4, dtype=torch.float32, device="cuda")
-            self.codes = torch.zeros(nb, dtype=torch.uint8, device="cuda")
-            self.data = torch.zeros(n // 2, dtype=torch.uint8, device="cuda")
-            self.scr = torch.zeros(L.bsq_frontend_scratch_bytes(ROWS, COLS), dtype=torch.uint8, device="cuda")
-            self.st = torch.zeros(4, dtype=torch.int32, device="cuda")
-
-    # Independent matrices are the unit of this workload, so the job keeps INFLIGHT of them in flight, each on a
-    # stream of its own with its own outputs (the stage entry point takes a stream): the tail of one matrix's
-    # kernels overlaps the head of the next one's.  One stream alone is measured too (single_stream_ms_per_step).
-    outs = [Outputs() for _ in range(INFLIGHT)]
-    streams = [torch.cuda.Stream() for _ in range(INFLIGHT)]
+    cfg = W.CONFIGS["C5A"]
+    rows, cols = cfg["rows"], cfg["cols"]
+    n = rows * cols
+    n_layers = args.layers or W.C5A_LAYERS
+    layers = shard.layers_for_rank(n_layers, rank, world)
+    cnt = len(layers)
+    mats = [W.config_matrix(torch, "C5A", layer=l) for l in layers]
+    lanes = max(1, min(args.lanes, max(cnt, 1)))
+    cfg_args = (rows, cols, cfg["outlier"], cfg["error"], cfg["rank"], cfg["niters"], cfg["uv"], cfg["s"], cfg["q"])
+    batch = L.bsq_batch_create(*cfg_args, lanes)
+    single = L.bsq_batch_create(*cfg_args, 1)
+    if not batch or not single:
+        raise RuntimeError("bsq_batch_create failed")
+    cap = int(L.bsq_lane_packed_capacity(L.bsq_batch_lane(batch, 0)))
+    VP = C.c_void_p * max(cnt, 1)
+    d_packed = [torch.empty(cap, dtype=torch.uint8, device="cuda") for _ in range(cnt)]
+    d_dst = [torch.empty((rows, cols), dtype=torch.float32, device="cuda") for _ in range(lanes)]
+    in_ptrs = VP(*[m.data_ptr() for m in mats])
+    packed_ptrs = VP(*[p.data_ptr() for p in d_packed])
+    dst_ptrs = VP(*[d_dst[i % lanes].data_ptr() for i in range(cnt)])
+    hdrs = (pkg.Array * max(cnt, 1))()
+    hdr_ptrs = VP(*[C.addressof(hdrs[i]) for i in range(cnt)])
+    sizes = (C.c_uint64 * max(cnt, 1))()
     main_stream = torch.cuda.current_stream()
-    o0 = outs[0]
-    d_idx, d_val, d_dq, d_codes, d_data, d_scr, d_st = o0.idx, o0.val, o0.dq, o0.codes, o0.data, o0.scr, o0.st
-    stream = main_stream.cuda_stream
 
-    def stage(i, lanes=INFLIGHT):
-        o = outs[i % lanes]
-        st = streams[i % lanes].cuda_stream if lanes > 1 else stream
-        rc = L.bsq_frontend_quantize(METHOD, d_in[i % NBUF].data_ptr(), ROWS, COLS, k, o.idx.data_ptr(), o.val.data_ptr(),
-                                     None, o.dq.data_ptr(), o.codes.data_ptr(), o.data.data_ptr(), o.scr.data_ptr(),
-                                     o.st.data_ptr(), st)
-        if rc != 0:
-            raise RuntimeError("bsq_frontend_quantize failed")
+    def compress_pass(b):
+        if cnt and L.bsq_batch_compress(b, in_ptrs, cnt, pkg.INPUT_DEVICE, packed_ptrs, cap, None, hdrs, sizes) != 0:
+            raise RuntimeError("bsq_batch_compress failed")
 
-    def timed_stage_loop(lanes):
-        """K steps, CUDA events on the main stream around them; the other streams are fenced by events on both sides."""
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    def decompress_pass(b):
+        if cnt and L.bsq_batch_decompress(b, hdr_ptrs, cnt, 1, dst_ptrs, n) != 0:
+            raise RuntimeError("bsq_batch_decompress failed")
+
+    def timed_steps(b, steps, passes):
+        """`steps` steps of `passes` passes each; returns (total ms, compress ms, decompress ms) from CUDA events."""
+        evs = []
         barrier()
-        e0.record(main_stream)
-        if lanes > 1:
-            for s_ in streams[:lanes]:
-                s_.wait_event(e0)
-        for i in range(args.steps):
-            stage(i, lanes)
-        if lanes > 1:
-            for s_ in streams[:lanes]:
-                main_stream.wait_stream(s_)
-        e1.record(main_stream)
+        for _ in range(steps * passes):
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            e[0].record(main_stream)
+            compress_pass(b)
+            e[1].record(main_stream)
+            decompress_pass(b)
+            e[2].record(main_stream)
+            evs.append(e)
         barrier()
-        return e0.elapsed_time(e1)
+        total = evs[0][0].elapsed_time(evs[-1][2])
+        return total, sum(e[0].elapsed_time(e[1]) for e in evs), sum(e[1].elapsed_time(e[2]) for e in evs)
 
-    # ---- device-stage throughput ----
-    for i in range(args.warmup):
-        stage(i)
-    for i in range(args.warmup):
-        stage(i, 1)
-    barrier()
+    # ---- warm-up, and how many passes a step needs for a timed region of at least 0.6 s ----
+    for _ in range(args.warmup):
+        compress_pass(batch)
+        decompress_pass(batch)
+    t_est, _, _ = timed_steps(batch, 1, 1)
+    t_est = shard.max_over_ranks([t_est], device="cuda")[0]
+    passes = max(1, int(math.ceil(600.0 / max(t_est * args.steps, 1e-3))))
+    err0 = rel_frob(mats[-1], d_dst[(cnt - 1) % lanes]) if cnt else None
+    packed_total = int(sum(sizes[i] for i in range(cnt)))
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    if args.stage_only:
-        ms_total = timed_stage_loop(1)
-        if rank == 0:
-            sampler.stop()
-            print(json.dumps({"stage_only": True, "ms_per_step": ms_total / args.steps}))
-        return
-    ms_total = timed_stage_loop(INFLIGHT)
-    ms_single = timed_stage_loop(1)
-    for o in outs:
-        if int(o.st[0]) != 0:
-            raise RuntimeError("kernel status word set: %d" % int(o.st[0]))
+    ms_total, ms_c, ms_d = timed_steps(batch, args.steps, passes)
 
-    # ---- per-pass durations for the roofline (events between the two kernels) ----
-    # Each timed call is queued behind three untimed steps on the same stream, so that the host has long enqueued the
-    # timed kernels when the GPU gets to their events: the intervals are kernel durations, not host launch latency.
-    ms_pass = (C.c_float * 2)()
-    p1, p2 = [], []
-    for i in range(max(8, min(args.steps, 24))):
-        for j in range(3):
-            stage(i + j + 1, 1)
-        rc = L.bsq_frontend_quantize_timed(METHOD, d_in[i % NBUF].data_ptr(), ROWS, COLS, k, d_idx.data_ptr(), d_val.data_ptr(),
-                                           None, d_dq.data_ptr(), d_codes.data_ptr(), d_data.data_ptr(), d_scr.data_ptr(),
-                                           d_st.data_ptr(), stream, ms_pass)
-        if rc != 0:
-            raise RuntimeError("bsq_frontend_quantize_timed failed")
-        p1.append(ms_pass[0])
-        p2.append(ms_pass[1])
-    ms_p1, ms_p2 = statistics.mean(p1), statistics.mean(p2)
+    # ---- one matrix at a time, with the big products timed on the lane's stream (roofline) ----
+    lane0 = L.bsq_batch_lane(single, 0)
+    L.bsq_lane_profile(lane0, 1)
+    prod_ms = []
+    one_c = one_d = 0.0
+    reps1 = max(1, min(cnt, 4))
+    ms_buf, kind_buf = (C.c_float * 32)(), (C.c_int * 32)()
+    for w in range(2):
+        for i in range(reps1):
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            torch.cuda.synchronize()
+            e[0].record(main_stream)
+            if L.bsq_lane_compress_begin(lane0, mats[i].data_ptr(), pkg.INPUT_DEVICE, d_packed[i].data_ptr(), cap) != 0 or \
+                    L.bsq_lane_compress_end(lane0, None, C.byref(hdrs[i]), None) != 0:
+                raise RuntimeError("lane compress failed")
+            e[1].record(main_stream)
+            if L.bsq_lane_decompress_begin(lane0, C.byref(hdrs[i]), 1, d_dst[0].data_ptr(), n) != 0 or L.bsq_lane_decompress_end(lane0) != 0:
+                raise RuntimeError("lane decompress failed")
+            e[2].record(main_stream)
+            torch.cuda.synchronize()
+            if w == 1:
+                one_c += e[0].elapsed_time(e[1]) / reps1
+                one_d += e[1].elapsed_time(e[2]) / reps1
+                k_ = L.bsq_lane_profile_read(lane0, ms_buf, kind_buf, 32)
+                prod_ms += [ms_buf[j] for j in range(k_) if kind_buf[j] == 0]
+    L.bsq_lane_profile(lane0, 0)
 
-    # ---- end to end through the public call: pinned host input, packed object back on the host ----
-    pinned = [torch.from_numpy(h).pin_memory() for h in host]
-    assert L.bsq_compress_initialize(ROWS, COLS, OUTLIER_RATIO, 0.0, -1, 1, pkg.NONE, pkg.NONE, METHOD, pkg.INPUT_HOST) == 0
+    # ---- end to end: pinned host matrices in, host objects out, decompress from the host objects ----
+    pinned = [torch.empty((rows, cols), dtype=torch.float32).pin_memory() for _ in range(cnt)]
+    for p, m in zip(pinned, mats):
+        p.copy_(m)
+    torch.cuda.synchronize()
+    host_ptrs = VP(*[p.data_ptr() for p in pinned])
+    outs = VP()
+    probe = torch.empty(1, dtype=torch.float32).pin_memory()
 
-    def e2e_step(i):
-        out = C.c_void_p(None)
-        if L.bsq_compress(pinned[i % NBUF].data_ptr(), C.byref(out), None) != 0:
-            raise RuntimeError("bitsqz_llm_compress failed")
-        size = int(L.bsq_get_packed_size(out))
-        L.bsq_free(out)
-        return size
-    for i in range(args.warmup):
-        packed_size = e2e_step(i)
+    def e2e_pass():
+        if cnt == 0:
+            return 0
+        if L.bsq_batch_compress(batch, host_ptrs, cnt, pkg.INPUT_HOST, None, 0, outs, None, sizes) != 0:
+            raise RuntimeError("bsq_batch_compress (host) failed")
+        if L.bsq_batch_decompress(batch, outs, cnt, 0, dst_ptrs, n) != 0:
+            raise RuntimeError("bsq_batch_decompress (host objects) failed")
+        probe.copy_(d_dst[(cnt - 1) % lanes].view(-1)[:1])            # the step's result is read back
+        got = sum(int(sizes[i]) for i in range(cnt))
+        for i in range(cnt):
+            L.bsq_free(outs[i])
+            outs[i] = None
+        return got
+    for _ in range(2):
+        e2e_pass()
     barrier()
     t0 = time.perf_counter()
-    for i in range(args.steps):
-        e2e_step(i)
+    for _ in range(args.steps * passes):
+        d2h = e2e_pass()
     torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
+    e2e_ms = (time.perf_counter() - t0) * 1e3
     barrier()
-    L.bsq_compress_release()
     clocks = sampler.stop() if rank == 0 else None
 
-    # ---- decompress (device stages: NF4_DQ dequantise + outlier scatter-add), reported beside ----
-    d_out = torch.zeros((ROWS, COLS), dtype=torch.float32, device="cuda")
-    douts = [torch.zeros((ROWS, COLS), dtype=torch.float32, device="cuda") for _ in range(NBUF)]
-
-    def dstage(i):
-        o = douts[i % NBUF]
-        L.bsq_dequantize_add_topk(METHOD, None, d_dq.data_ptr(), d_codes.data_ptr(), d_data.data_ptr(), ROWS, COLS,
-                                  d_idx.data_ptr(), d_val.data_ptr(), k, o.data_ptr(), d_st.data_ptr(), stream)
-    for i in range(args.warmup):
-        dstage(i)
-    barrier()
-    d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    d0.record()
-    for i in range(args.steps):
-        dstage(i)
-    d1.record()
-    barrier()
-    ms_dec = d0.elapsed_time(d1)
-    del d_out
-
-    # ---- max over ranks ----
-    import importlib.util
-    spec = importlib.util.spec_from_file_location("bsq_shard", os.path.join(entry.PKG_DIR, "shard.py"))
-    shard = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(shard)
-    ms_total, e2e_ms, ms_dec, ms_p1, ms_p2, ms_single = shard.max_over_ranks([ms_total, e2e_s * 1e3, ms_dec, ms_p1, ms_p2, ms_single], device="cuda")
+    ms_total, ms_c, ms_d, e2e_ms, one_c, one_d = shard.max_over_ranks([ms_total, ms_c, ms_d, e2e_ms, one_c, one_d], device="cuda")
+    packed_all = int(sum(shard.gather_objects(packed_total)))
+    L.bsq_batch_destroy(batch)
+    L.bsq_batch_destroy(single)
+    del pinned, d_packed
 
     if rank == 0:
-        in_bytes = n * 4
-        value = world * in_bytes * args.steps / (ms_total * 1e-3) / 1e9
-        e2e_value = world * in_bytes * args.steps / (e2e_ms * 1e-3) / 1e9
-        dec_value = world * in_bytes * args.steps / (ms_dec * 1e-3) / 1e9
-        peak, peak_kind = measured_peaks()
-        # algorithmic bytes: pass 1 reads the matrix once and writes k (u16, f32) pairs per row and one
-        # float per 64-element block; the whole stage adds the nibbles and one scale byte per block
-        bytes_p1 = in_bytes + ROWS * k * 6 + nb * 4
-        bytes_stage = in_bytes + ROWS * k * 6 + n // 2 + nb + 4
-        ach_p1 = bytes_p1 / (ms_p1 * 1e-3) / 1e9
-        ach_stage = bytes_stage / ((ms_total / args.steps) * 1e-3) / 1e9
+        hbm_peak, bf16_peak, peak_kind = measured_peaks()
+        tf32 = tf32_peak(torch)
+        batch_bytes = n_layers * n * 4
+        per_step = batch_bytes * passes
+        nsteps = args.steps
+        value = per_step * nsteps / (ms_total * 1e-3) / 1e9
+        flops = 2.0 * rows * cols * cfg["rank"]
+        prod_mean = statistics.mean(prod_ms) if prod_ms else None
+        # products alternate: W X (W read along M: A as stored is K x M) and W^T X (A read along K)
+        ach = flops / (prod_mean * 1e-3) / 1e12 if prod_mean else None
+        peak3 = tf32 / 3.0
         line = {
-            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "configs[1]: 4096x4096 FP32 device matrix, outlier_topk=0.01 (k=41/row), NF4_DQ, no SVD",
-                       "rows": ROWS, "cols": COLS, "k": int(k),
-                       "parallelism": f"independent matrices x{world} GPU(s), {INFLIGHT} in flight per GPU on separate streams",
-                       "single_stream_ms_per_step": ms_single / args.steps,
-                       "l2": f"inputs rotate over {NBUF} x 64 MiB matrices (256 MiB > 126 MB L2)"},
-            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": int(packed_size),
-                    "api": "bitsqz_llm_compress, BITSQZ_LLM_INPUT_HOST, pinned input"},
-            "decompress": {"value": dec_value, "unit": "GB/s (FP32 output)", "ms_per_step": ms_dec / args.steps,
-                           "stages": "nf4dq dequantise + outlier scatter-add in one kernel, device resident"},
-            "gpu_launches": 2 * args.steps,
-            "roofline": {"bound": "hbm", "kernel": "frontend_select_kernel<4> (4 warps per row)", "achieved": ach_p1, "peak": peak,
-                         "peak_kind": peak_kind, "unit": "GB/s", "frac": ach_p1 / peak, "traffic": NCU_TRAFFIC_SELECT,
-                         "ms_per_launch": ms_p1, "pass2_ms_per_launch": ms_p2,
-                         "stage": {"achieved": ach_stage, "frac": ach_stage / peak, "bytes": bytes_stage}},
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": nsteps, "warmup": args.warmup,
+            "ms_per_step": ms_total / nsteps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32 (products as 3xTF32 on tcgen05, FP32-level accuracy)", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "rows": rows, "cols": cols, "layers": n_layers, "passes_per_step": passes,
+                       "lanes_per_gpu": lanes,
+                       "parallelism": "matrix i on rank i %% %d, no collective on the data path; %d matrices in flight per GPU" % (world, lanes),
+                       "l2": "every input matrix is 235 MB (> 126 MB L2)",
+                       "timed_region_s": ms_total * 1e-3},
+            "compress": {"value": per_step * nsteps / (ms_c * 1e-3) / 1e9, "unit": "GB/s", "ms_per_matrix": ms_c / (nsteps * passes * max(cnt, 1)),
+                         "one_at_a_time_ms_per_matrix": one_c},
+            "decompress": {"value": per_step * nsteps / (ms_d * 1e-3) / 1e9, "unit": "GB/s (FP32 output)",
+                           "ms_per_matrix": ms_d / (nsteps * passes * max(cnt, 1)), "one_at_a_time_ms_per_matrix": one_d,
+                           "call": "bsq_batch_decompress on device-resident objects"},
+            "rel_frob_last_layer": err0,
+            "packed_bytes_per_step": packed_all * passes, "compression_ratio": batch_bytes / max(packed_all, 1),
+            "e2e": {"value": per_step * nsteps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": per_step + packed_all * passes,
+                    "d2h_bytes_per_step": packed_all * passes + 4 * passes * world, "ms_per_step": e2e_ms / nsteps,
+                    "api": "bsq_batch_compress (pinned host matrices -> host objects) + bsq_batch_decompress (host objects -> device "
+                           "matrix), the lanes form of bitsqz_llm_compress / bitsqz_llm_decompress; h2d = inputs + objects on their way "
+                           "back for decompress"},
+            "gpu_launches": (LAUNCHES_PER_COMPRESS + LAUNCHES_PER_DECOMPRESS) * n_layers * passes * nsteps,
+            "roofline": {"bound": "tensor", "kernel": "gemm_tc_image_kernel<*,256> (tcgen05 3xTF32, 4096x14336 matrix times a 256-column panel)",
+                         "achieved": ach, "peak": peak3, "unit": "TFLOP/s", "frac": (ach / peak3) if ach else None, "traffic": None,
+                         "peak_kind": "TF32 dense matmul measured in this run (%.0f TFLOP/s) / 3; BF16 %s %.0f" % (tf32, peak_kind, bf16_peak),
+                         "flops_per_launch": flops, "ms_per_launch": prod_mean, "launches_timed": len(prod_ms),
+                         "ms_w_x": statistics.mean(prod_ms[0::2]) if prod_ms else None,
+                         "ms_wt_x": statistics.mean(prod_ms[1::2]) if prod_ms else None,
+                         "timed": "CUDA events on the lane's stream around each product, one matrix in flight"},
             "clocks": clocks,
         }
-        if world == 1:
-            orc = entry.load_oracle()
-            step, kind, cores, desc = cpu_pipeline(orc)
-            step(host[0])
-            reps, t0 = 0, time.perf_counter()
-            while reps < 3 or (time.perf_counter() - t0 < 10.0 and reps < 200):
-                step(host[reps % NBUF])
-                reps += 1
-            dt = time.perf_counter() - t0
-            line["cpu_baseline"] = {"value": in_bytes * reps / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
-                                    "sample": f"{reps} full matrices in {dt:.1f} s; {desc}"}
+        if not args.skip_extras:
+            line["configs1_frontend"] = c2_frontend_leg(torch, pkg, L, W, hbm_peak)
+            if world == 1:
+                line["cpu_baseline"] = cpu_nf4_baseline(W)
         print(json.dumps(line))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

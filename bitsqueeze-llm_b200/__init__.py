@@ -81,12 +81,29 @@ SIGNATURES = {
     "bsq_frontend_quantize_timed": (_i, [_i, _vp, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bsq_residual_error": (_i, [_vp, _vp, _u64, _vp, _vp, _vp]),
     "bsq_svd_lowrank": (_i, [_vp, _i, _i, _i, _i, C.c_ulonglong, _vp, _vp, _vp, _vp]),
-    "bsq_reconstruct": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "bsq_reconstruct": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "bsq_gemm": (_i, [_i, _i, _vp, C.c_long, _vp, C.c_long, _vp, C.c_long, _i, _i, _i, _vp, _sz, _i, _vp, _vp]),
     "bsq_shard_unique_id": (_i, [_vp, _sz]),
     "bsq_shard_comm_create": (_vp, [_vp, _i, _i]),
     "bsq_shard_comm_destroy": (None, [_vp]),
     "bsq_svd_lowrank_sharded": (_i, [_vp, _vp, _i, _i, _i, _i, _i, C.c_ulonglong, _vp, _vp, _vp, _vp]),
+    "bsq_lane_create": (_vp, [_u16, _u16, _f, _f, _i, _i, _i, _i, _i]),
+    "bsq_lane_destroy": (None, [_vp]),
+    "bsq_lane_packed_capacity": (_u64, [_vp]),
+    "bsq_lane_stream": (_vp, [_vp, _i]),
+    "bsq_lane_compress_begin": (_i, [_vp, _vp, _i, _vp, _u64]),
+    "bsq_lane_compress_end": (_i, [_vp, C.POINTER(_vp), _vp, C.POINTER(_u64)]),
+    "bsq_lane_decompress_begin": (_i, [_vp, _vp, _i, _vp, _u64]),
+    "bsq_lane_decompress_end": (_i, [_vp]),
+    "bsq_lane_profile": (_i, [_vp, _i]),
+    "bsq_lane_profile_read": (_i, [_vp, _vp, _vp, _i]),
+    "bsq_batch_create": (_vp, [_u16, _u16, _f, _f, _i, _i, _i, _i, _i, _i]),
+    "bsq_batch_destroy": (None, [_vp]),
+    "bsq_batch_lanes": (_i, [_vp]),
+    "bsq_batch_lane": (_vp, [_vp, _i]),
+    "bsq_batch_compress": (_i, [_vp, C.POINTER(_vp), _i, _i, C.POINTER(_vp), _u64, C.POINTER(_vp), _vp, C.POINTER(_u64)]),
+    "bsq_batch_decompress": (_i, [_vp, C.POINTER(_vp), _i, _i, C.POINTER(_vp), _u64]),
+    "bsq_test_inject_status": (None, [_i, _u32]),
     "bsq_build_info": (C.c_char_p, []),
 }
 

@@ -140,10 +140,10 @@ int bsq_gemm(int a_kmajor, int b_kmajor, const float *d_A, long lda, const float
                           nullptr, 0, nullptr, d_status, d_workspace, workspace_bytes, device_sm_count(), as_stream(stream)));
 }
 int bsq_reconstruct(const float *d_U, const float *d_S, const float *d_V, int m, int n, int k, const float *d_minuend,
-                    float *d_out, uint32_t *d_flag, void *stream) {
+                    float *d_out, uint32_t *d_flag, uint32_t *d_status, void *stream) {
     if (!d_U || !d_S || !d_V || !d_out || m <= 0 || n <= 0 || k <= 0) return 1;
     if (d_minuend && !d_flag) return 1;
-    return rc(reconstruct_lowrank(d_U, d_S, d_V, m, n, k, d_minuend, d_out, d_flag, device_sm_count(), as_stream(stream)));
+    return rc(reconstruct_lowrank(d_U, d_S, d_V, m, n, k, d_minuend, d_out, d_flag, d_status, device_sm_count(), as_stream(stream)));
 }
 
 const char *bsq_build_info(void) { return "bitsqz_llm sm_100a " __DATE__; }

@@ -94,12 +94,17 @@ void svd_workspace_destroy(SvdWorkspace *ws);
 // A row-major m x n -> U (m x k row-major), S (k, descending), V (n x k row-major).
 cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d_S, float *d_V,
                         unsigned long long seed, unsigned *d_status, cudaStream_t stream);
+// Optional timing of a call's products with the big matrix (kind 0) and, row-sharded, its all-reduces (kind 1).
+cudaError_t svd_workspace_profile(SvdWorkspace *ws, bool on);
+int svd_workspace_spans(SvdWorkspace *ws, float *ms, int *kinds, int capacity);
 // For calls made with d_status == nullptr: waits for the stream and returns an error if a bounded wait gave up.
 cudaError_t svd_workspace_finish(SvdWorkspace *ws, cudaStream_t stream);
 // out = (U diag(S)) V^T, row-major m x n.  d_minuend (nullable): write minuend - out instead and
 // OR 1 into *d_flag when some |difference| > FLT_EPSILON.
+// d_status (nullable): device word that receives kStatusBarrierTimeout if a bounded wait of the product kernel gives up
+// (the output is then incomplete).
 cudaError_t reconstruct_lowrank(const float *d_U, const float *d_S, const float *d_V, int m, int n, int k,
-                                const float *d_minuend, float *d_out, unsigned *d_flag, int sm_count,
+                                const float *d_minuend, float *d_out, unsigned *d_flag, unsigned *d_status, int sm_count,
                                 cudaStream_t stream);
 
 }  // namespace bsq

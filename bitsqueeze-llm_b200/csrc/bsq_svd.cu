@@ -16,8 +16,9 @@
 //     shorter than unit length instead of dividing by zero;
 //   * the small SVD works on a k x k core: B^T = Q2 C with C = R2 R1 the product of the two
 //     triangular factors, C = Uc S Vc^T, V_hat = Q2 Uc, U = Q Vc.
-// The SVD of the k x k core is a cuSOLVER call for now (gesvdj); everything else, in particular
-// everything that touches an M- or N-sized array, is a kernel of this library.
+// The SVD of the k x k core is a one-sided Jacobi kernel of this library up to 256 columns (one CTA up to 64, a
+// thread-block cluster above); larger cores, and devices that cannot place the cluster, go to cuSOLVER's gesvdj on
+// the k x k core.  Everything that touches an M- or N-sized array is a kernel of this library.
 // Omega comes from cuRAND's XORWOW generator like the reference's (svd_lowrank_cuda.cu:143,289-291),
 // seeded per call, column-major N x k.
 #include "bsq_device.cuh"
@@ -62,6 +63,13 @@ struct SvdWorkspace {
     bool own_core_svd = false;          // k small enough for jacobi_svd_kernel (else cuSOLVER's gesvdj on the core)
     bool seeded = false;                // omega holds the draw for `seed`
     unsigned long long seed = 0;
+    // optional timing of the spans that matter for a roofline: the products with the big matrix (kind 0) and the
+    // all-reduces of the row-sharded mode (kind 1), bracketed by events on the call's stream
+    static constexpr int kMaxSpans = 32;
+    bool profile = false;
+    int spans = 0;
+    int span_kind[kMaxSpans] = {};
+    cudaEvent_t span_ev[2 * kMaxSpans] = {};
 };
 
 namespace {
@@ -889,6 +897,24 @@ void jacobi_cluster_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, i
     cfg->numAttrs = 1;
 }
 
+// A timed span of the current call (no-ops unless the workspace's profiling is on).
+int span_begin(SvdWorkspace *ws, int kind, cudaStream_t st) {
+    if (!ws->profile || ws->spans >= SvdWorkspace::kMaxSpans) return -1;
+    const int i = ws->spans++;
+    ws->span_kind[i] = kind;
+    cudaEventRecord(ws->span_ev[2 * i], st);
+    return i;
+}
+void span_end(SvdWorkspace *ws, int i, cudaStream_t st) {
+    if (i >= 0) cudaEventRecord(ws->span_ev[2 * i + 1], st);
+}
+cudaError_t timed_allreduce(SvdWorkspace *ws, float *buf, size_t count, cudaStream_t st) {
+    const int sp = span_begin(ws, 1, st);
+    const cudaError_t err = ws->allreduce(ws->allreduce_ctx, buf, count, st);
+    span_end(ws, sp, st);
+    return err;
+}
+
 bool alloc_f(float **p, size_t count) {
     if (cudaMalloc(reinterpret_cast<void **>(p), std::max<size_t>(count, 1) * sizeof(float)) != cudaSuccess) {
         cudaGetLastError();
@@ -913,8 +939,7 @@ cudaError_t orthonormalise(SvdWorkspace *ws, float *Y, float *tmp, int rows, int
         if (err != cudaSuccess) return err;
         // a row-sharded panel: its Gram matrix is the sum of the shards' (the one exchange per QR pass);
         // every rank then factors the same k x k matrix and gets bit-identical R
-        if (sharded_rows && ws->allreduce && (err = ws->allreduce(ws->allreduce_ctx, ws->g, (size_t)k * k, st)) != cudaSuccess)
-            return err;
+        if (sharded_rows && ws->allreduce && (err = timed_allreduce(ws, ws->g, (size_t)k * k, st)) != cudaSuccess) return err;
         if (k <= kCholeskyBlockedMaxK) {
             cholesky_inverse_blocked_kernel<<<1, 1024, cholesky_blocked_smem_bytes(k), st>>>(ws->g, k, ws->t,
                                                                                                 pass == 0 ? r_a : r_b);
@@ -944,11 +969,12 @@ cudaError_t times_w(SvdWorkspace *ws, const float *A, bool w_transposed_product,
     const int rows_out = w_transposed_product ? ws->N : ws->M;
     const int contract = w_transposed_product ? ws->M : ws->N;
     const long ldx = x_colmajor ? contract : ws->k;
+    const int sp = span_begin(ws, 0, st);
     cudaError_t err = gemm(use_a_as_stored, x_colmajor, A, ws->n, X, ldx, C, ws->k, rows_out, ws->k, contract, nullptr,
                            nullptr, 0, nullptr, ws->status, ws->gemm_ws, ws->gemm_ws_bytes, ws->sm_count, st);
+    span_end(ws, sp, st);
     // row-sharded W: W^T X contracts over the sharded rows, so the shards' partial products are summed
-    if (err == cudaSuccess && w_transposed_product && ws->allreduce)
-        err = ws->allreduce(ws->allreduce_ctx, C, (size_t)rows_out * ws->k, st);
+    if (err == cudaSuccess && w_transposed_product && ws->allreduce) err = timed_allreduce(ws, C, (size_t)rows_out * ws->k, st);
     return err;
 }
 
@@ -1057,11 +1083,37 @@ void svd_workspace_destroy(SvdWorkspace *ws) {
         if (p) cudaFree(p);
     if (ws->dev_info) cudaFree(ws->dev_info);
     if (ws->own_status) cudaFree(ws->own_status);
+    for (cudaEvent_t e : ws->span_ev)
+        if (e) cudaEventDestroy(e);
     if (ws->svdj) cusolverDnDestroyGesvdjInfo(ws->svdj);
     if (ws->solver) cusolverDnDestroy(ws->solver);
     if (ws->rng) curandDestroyGenerator(ws->rng);
     cudaGetLastError();
     delete ws;
+}
+
+// Timing of the big products and all-reduces of the calls that follow (events on the call's stream).
+cudaError_t svd_workspace_profile(SvdWorkspace *ws, bool on) {
+    if (!ws) return cudaErrorInvalidValue;
+    if (on)
+        for (cudaEvent_t &e : ws->span_ev)
+            if (!e && cudaEventCreate(&e) != cudaSuccess) return cudaErrorUnknown;
+    ws->profile = on;
+    ws->spans = 0;
+    return cudaSuccess;
+}
+// Durations of the last call's spans, in call order; the call's stream must have been waited for.
+int svd_workspace_spans(SvdWorkspace *ws, float *ms, int *kinds, int capacity) {
+    if (!ws || !ws->profile) return 0;
+    int n = 0;
+    for (int i = 0; i < ws->spans && n < capacity; ++i) {
+        float t = 0.0f;
+        if (cudaEventElapsedTime(&t, ws->span_ev[2 * i], ws->span_ev[2 * i + 1]) != cudaSuccess) { cudaGetLastError(); continue; }
+        if (ms) ms[n] = t;
+        if (kinds) kinds[n] = ws->span_kind[i];
+        ++n;
+    }
+    return n;
 }
 
 // Waits for the stream and reads the workspace's own status word (calls made without a caller status word).
@@ -1077,6 +1129,7 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
                         unsigned *d_status, cudaStream_t st) {
     if (!ws || !d_A || !d_U || !d_S || !d_V) return cudaErrorInvalidValue;
     const int k = ws->k;
+    ws->spans = 0;
     ws->status = d_status ? d_status : ws->own_status;    // bounded waits of the tensor-core GEMMs report here
     if (!d_status && cudaMemsetAsync(ws->own_status, 0, sizeof(unsigned), st) != cudaSuccess) return cudaErrorUnknown;
     if (curandSetStream(ws->rng, st) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
@@ -1146,10 +1199,11 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
 }
 
 cudaError_t reconstruct_lowrank(const float *d_U, const float *d_S, const float *d_V, int m, int n, int k,
-                                const float *d_minuend, float *d_out, unsigned *d_flag, int sm_count, cudaStream_t st) {
+                                const float *d_minuend, float *d_out, unsigned *d_flag, unsigned *d_status, int sm_count,
+                                cudaStream_t st) {
     if (!d_U || !d_S || !d_V || !d_out || m <= 0 || n <= 0 || k <= 0) return cudaErrorInvalidValue;
     // out(i, j) = sum_t (U(i, t) S(t)) V(j, t): A = U as stored with a per-k scale, B = V^T (K-major)
-    return gemm(true, true, d_U, k, d_V, k, d_out, n, m, n, k, d_S, d_minuend, n, d_flag, nullptr, nullptr, 0, sm_count, st);
+    return gemm(true, true, d_U, k, d_V, k, d_out, n, m, n, k, d_S, d_minuend, n, d_flag, d_status, nullptr, 0, sm_count, st);
 }
 
 }  // namespace bsq

@@ -128,9 +128,10 @@ int bsq_residual_error(const float *d_a, const float *d_b, uint64_t n, float *d_
 int bsq_svd_lowrank(const float *d_A, int m, int n, int k, int niter, unsigned long long seed, float *d_U, float *d_S,
                     float *d_V, void *stream);
 /* reconstruct_lowrank_cuda (reconstruct_lowrank_cuda.cuh:73-78): d_out = (U diag(S)) V^T.
- * d_minuend non-NULL: d_out = d_minuend - (U diag(S)) V^T and *d_flag |= any(|d_out| > FLT_EPSILON). */
+ * d_minuend non-NULL: d_out = d_minuend - (U diag(S)) V^T and *d_flag |= any(|d_out| > FLT_EPSILON).
+ * d_status (nullable) receives bit 0 if a bounded wait inside the product kernel gave up (d_out is then incomplete). */
 int bsq_reconstruct(const float *d_U, const float *d_S, const float *d_V, int m, int n, int k, const float *d_minuend,
-                    float *d_out, uint32_t *d_flag, void *stream);
+                    float *d_out, uint32_t *d_flag, uint32_t *d_status, void *stream);
 
 /* The FP32 matrix product inside the two stages above, where the reference calls cublasSgemm
  * (svd_lowrank_cuda.cu:293-309, reconstruct_lowrank_cuda.cu:46-61): C[M x N] = opA[M x K] * opB[K x N], all row-major
@@ -154,6 +155,64 @@ void *bsq_shard_comm_create(const void *unique_id, int rank, int world);
 void bsq_shard_comm_destroy(void *comm);
 int bsq_svd_lowrank_sharded(void *comm, const float *d_A_local, int m_local, int m_total, int n, int k, int niter,
                             unsigned long long seed, float *d_U_local, float *d_S, float *d_V, void *stream);
+
+/* ---- lanes and batches: several independent matrices in flight on one device -----------------------------------
+ * No counterpart in the reference, whose compress and decompress calls are synchronous and keep one pair of runtimes
+ * per process (src/bitsqz_llm.cu:981-1302, 1304-1393 are the calls these split in two).  A lane owns a compress and a
+ * decompress runtime of one configuration on the device that was current when it was created, with a CUDA stream of
+ * its own.  "begin" enqueues a whole call on that stream and returns; "end" waits for the stream and finishes the
+ * result.  Calls begun on different lanes overlap on the GPU.  One compress or decompress call per lane at a time;
+ * lanes are not thread-safe (one host thread per lane, or one for all).
+ *
+ * Results of compress go to a pooled pinned host object exactly like bitsqz_llm_compress (d_packed NULL) or, with
+ * d_packed set, to a device buffer of at least bsq_lane_packed_capacity() bytes that receives the same bytes in the
+ * same layout (200-byte header, then the payload): copying packed_size bytes from it to the host gives a buffer that
+ * load_bitsqz_llm_from_buffer accepts.  For such a device-resident object bsq_lane_compress_end fills *device_header,
+ * a host copy of the header whose `payload` member is the DEVICE address of the payload; pass that header to
+ * bsq_lane_decompress_begin with payload_on_device = 1. */
+typedef struct bsq_lane bsq_lane_t;
+bsq_lane_t *bsq_lane_create(uint16_t num_rows, uint16_t num_columns, float outlier_topk_ratio, float error_correction_topk_ratio,
+                            int svd_ranks, int svd_niters, int svd_uv_format, int svd_s_format, int quantization_only_format);
+void bsq_lane_destroy(bsq_lane_t *lane);
+/* upper bound of the packed size (header + payload) of this lane's configuration */
+uint64_t bsq_lane_packed_capacity(bsq_lane_t *lane);
+/* the lane's cudaStream_t (compress side or decompress side), e.g. to make other work wait for it with an event */
+void *bsq_lane_stream(bsq_lane_t *lane, int decompress_side);
+/* matrix: host (input_location 0; pinned memory makes the copy asynchronous) or device (1) */
+int bsq_lane_compress_begin(bsq_lane_t *lane, const float *matrix, int input_location, void *d_packed, uint64_t capacity);
+/* host object: *out (must be NULL on entry) receives it, release with bsq_free; device object: device_header (nullable) */
+int bsq_lane_compress_end(bsq_lane_t *lane, struct bitsqz_llm_array **out, struct bitsqz_llm_array *device_header,
+                          uint64_t *packed_size);
+int bsq_lane_decompress_begin(bsq_lane_t *lane, const struct bitsqz_llm_array *header, int payload_on_device, float *d_dst,
+                              uint64_t dst_num_elements);
+int bsq_lane_decompress_end(bsq_lane_t *lane);
+/* Measurement aid for lanes with an SVD stage: with `on`, the compress calls that follow bracket every product with
+ * the big matrix (kind 0) by CUDA events on the lane's stream; after bsq_lane_compress_end, bsq_lane_profile_read
+ * returns how many spans the last call had and their milliseconds, in call order. */
+int bsq_lane_profile(bsq_lane_t *lane, int on);
+int bsq_lane_profile_read(bsq_lane_t *lane, float *ms, int *kinds, int capacity);
+
+/* A batch is `lanes` lanes (1..16) of one configuration; matrix i of a call runs on lane i % lanes, so up to `lanes`
+ * matrices are in flight.  bsq_batch_compress: d_packed NULL -> outs[i] receive host objects (bsq_free each);
+ * d_packed set -> object i goes to the device buffer d_packed[i] (capacity bytes each), device_headers[i] and
+ * packed_sizes[i] (both nullable arrays) describe it.  Matrices are independent, results do not depend on the lane. */
+typedef struct bsq_batch bsq_batch_t;
+bsq_batch_t *bsq_batch_create(uint16_t num_rows, uint16_t num_columns, float outlier_topk_ratio, float error_correction_topk_ratio,
+                              int svd_ranks, int svd_niters, int svd_uv_format, int svd_s_format, int quantization_only_format,
+                              int lanes);
+void bsq_batch_destroy(bsq_batch_t *batch);
+int bsq_batch_lanes(bsq_batch_t *batch);
+bsq_lane_t *bsq_batch_lane(bsq_batch_t *batch, int i);
+int bsq_batch_compress(bsq_batch_t *batch, const float *const *matrices, int count, int input_location, void *const *d_packed,
+                       uint64_t capacity, struct bitsqz_llm_array **outs, struct bitsqz_llm_array *device_headers,
+                       uint64_t *packed_sizes);
+int bsq_batch_decompress(bsq_batch_t *batch, const struct bitsqz_llm_array *const *headers, int count, int payload_on_device,
+                         float *const *d_dsts, uint64_t dst_num_elements);
+
+/* Test hook (no counterpart in the reference): the next bsq_compress (which = 0) or bsq_decompress (which = 1) on the
+ * current device starts with `bits` set in its device status word, as if a kernel had reported them; that call must
+ * return 1.  Lets the error path be tested without making a kernel fail. */
+void bsq_test_inject_status(int which, uint32_t bits);
 
 /* library build tag: "sm_100a" plus the compile date */
 const char *bsq_build_info(void);

@@ -541,6 +541,15 @@ int bsq_oracle_decompress_nosvd(const uint8_t *packed, uint64_t size, float *out
     return 0;
 }
 
+void bsq_oracle_set_threads(int n) {
+#ifdef _OPENMP
+    extern void omp_set_num_threads(int);
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int bsq_oracle_max_threads(void) {
 #ifdef _OPENMP
     extern int omp_get_max_threads(void);

@@ -72,6 +72,9 @@ class Oracle:
     def max_threads(self):
         return int(self.lib.bsq_oracle_max_threads())
 
+    def set_threads(self, n):
+        self.lib.bsq_oracle_set_threads(int(n))
+
     def nf4_code(self, v):
         return int(self.lib.bsq_oracle_nf4_code(C.c_float(v)))
 
@@ -184,6 +187,9 @@ class RefCpu:
 
     def max_threads(self):
         return int(self.lib.ref_cpu_max_threads())
+
+    def set_threads(self, n):
+        self.lib.ref_cpu_set_threads(int(n))
 
     def nf4_quantize(self, x):
         x = _f32(x).ravel()

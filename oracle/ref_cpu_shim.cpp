@@ -82,4 +82,13 @@ int ref_cpu_max_threads(void) {
 #endif
 }
 
+// OpenMP threads for the calls that follow (a launcher may have exported OMP_NUM_THREADS=1 to the process)
+void ref_cpu_set_threads(int n) {
+#ifdef _OPENMP
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 }  // extern "C"

@@ -48,7 +48,7 @@ def test_reconstruct_matches_fp64(lib, oracle, shape):
     v = rng.standard_normal((n, k)).astype(np.float32)
     want = oracle.reconstruct(u, s, v)
     d_out = torch.zeros((m, n), dtype=torch.float32, device="cuda")
-    assert lib.bsq_reconstruct(dev(u).data_ptr(), dev(s).data_ptr(), dev(v).data_ptr(), m, n, k, None, d_out.data_ptr(), None, None) == 0
+    assert lib.bsq_reconstruct(dev(u).data_ptr(), dev(s).data_ptr(), dev(v).data_ptr(), m, n, k, None, d_out.data_ptr(), None, None, None) == 0
     torch.cuda.synchronize()
     # FP32 accumulation over k terms against FP64: relative Frobenius error <= 1e-6
     assert rel_frob(want, d_out.cpu().numpy()) <= 1e-6
@@ -56,7 +56,7 @@ def test_reconstruct_matches_fp64(lib, oracle, shape):
     r = want + np.float32(0.25)
     d_flag = torch.zeros(4, dtype=torch.int32, device="cuda")
     assert lib.bsq_reconstruct(dev(u).data_ptr(), dev(s).data_ptr(), dev(v).data_ptr(), m, n, k, dev(r).data_ptr(),
-                               d_out.data_ptr(), d_flag.data_ptr(), None) == 0
+                               d_out.data_ptr(), d_flag.data_ptr(), None, None) == 0
     torch.cuda.synchronize()
     assert int(d_flag[0]) == 1
     assert np.allclose(d_out.cpu().numpy(), 0.25, atol=1e-4 * max(1.0, float(np.abs(want).max())))
