@@ -382,6 +382,110 @@ def c2_frontend_leg(torch, pkg, L, W, hbm_peak):
                            "frac_of_hbm_peak": ach_d / hbm_peak, "kernel": "dequantise + outlier add in one kernel"}}
 
 
+def row_sharded_leg(torch, dist, pkg, L, W, rank, world):
+    """The second half of configs[4]: one 65536 x 4096 matrix (seeded, configuration 3's construction) held as `world`
+    row shards, rank-128 randomized SVD with 2 power iterations; NCCL all-reduces of the k x k Gram matrices and the
+    n x k partial products are the only exchange.  First a smaller matrix (32768 rows, which one GPU can also take
+    unsharded) for parity, then the full one for time; every rank also packs its shard as an ordinary object and
+    decompresses it through the unchanged public call."""
+    cfg = W.C5B
+    n, k, niter = cfg["cols"], cfg["rank"], cfg["niters"]
+    ids = [None]
+    if rank == 0:
+        buf = (C.c_char * 128)()
+        if L.bsq_shard_unique_id(buf, 128) != 0:
+            raise RuntimeError("bsq_shard_unique_id failed (NCCL not found)")
+        ids = [bytes(buf)]
+    dist.broadcast_object_list(ids, src=0)
+    comm = L.bsq_shard_comm_create(ids[0], rank, world)
+    if not comm:
+        raise RuntimeError("bsq_shard_comm_create failed")
+    out = {"workload": "65536x4096 FP32 (G1 diag(1/i) G2^T + 0.01 N(0,1)), rank 128, 2 power iterations, %d row shards" % world}
+
+    def sq_sums(a, u, s, v):
+        r = a.double() - (u.double() * s.double()) @ v.double().T
+        t = torch.stack([(r * r).sum(), (a.double() ** 2).sum()])
+        dist.all_reduce(t)
+        return float((t[0] / t[1]).sqrt())
+
+    def run(m_total, timed_calls):
+        m_local = m_total // world
+        a = W.lowrank_matrix(torch, m_total, n, cfg["seed"], row_slice=(rank * m_local, m_local))
+        u = torch.zeros((m_local, k), device="cuda")
+        s = torch.zeros(k, device="cuda")
+        v = torch.zeros((n, k), device="cuda")
+        h = L.bsq_shard_svd_create(comm, m_local, m_total, n, k, niter)
+        if not h:
+            raise RuntimeError("bsq_shard_svd_create failed")
+        stream = torch.cuda.current_stream().cuda_stream
+        res = {}
+        for _ in range(2):
+            if L.bsq_shard_svd_run(h, a.data_ptr(), 1241, u.data_ptr(), s.data_ptr(), v.data_ptr(), stream) != 0:
+                raise RuntimeError("bsq_shard_svd_run failed")
+        res["rel_frob"] = sq_sums(a, u, s, v)
+        if timed_calls:
+            L.bsq_shard_svd_profile(h, 1)
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(timed_calls):
+                if L.bsq_shard_svd_run(h, a.data_ptr(), 1241, u.data_ptr(), s.data_ptr(), v.data_ptr(), stream) != 0:
+                    raise RuntimeError("bsq_shard_svd_run failed")
+            e1.record()
+            torch.cuda.synchronize()
+            ms, kinds = (C.c_float * 32)(), (C.c_int * 32)()
+            cnt = L.bsq_shard_svd_profile_read(h, ms, kinds, 32)
+            t = torch.tensor([e0.elapsed_time(e1) / timed_calls, sum(ms[i] for i in range(cnt) if kinds[i] == 1),
+                              sum(ms[i] for i in range(cnt) if kinds[i] == 0)], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            res["ms_per_call"], res["allreduce_ms_per_call"], res["big_products_ms_per_call"] = [float(x) for x in t]
+            res["allreduces_per_call"] = sum(1 for i in range(cnt) if kinds[i] == 1)
+            res["fp32_input_gbs"] = m_total * n * 4 / (res["ms_per_call"] * 1e-3) / 1e9
+            # the shard as an ordinary object, through the unchanged decompress
+            obj = C.c_void_p(None)
+            if L.bsq_shard_compress(h, a.data_ptr(), 1241, C.byref(obj), stream) != 0:
+                raise RuntimeError("bsq_shard_compress failed")
+            if L.bsq_decompress_initialize(m_local, n, 0.0, 0.0, k, -1, -1, -1) != 0:
+                raise RuntimeError("decompress initialise failed")
+            y = torch.zeros((m_local, n), device="cuda")
+            if L.bsq_decompress(obj, y.data_ptr(), m_local * n) != 0:
+                raise RuntimeError("shard object did not decompress")
+            torch.cuda.synchronize()
+            r = (a.double() - y.double())
+            t2 = torch.stack([(r * r).sum(), (a.double() ** 2).sum()])
+            dist.all_reduce(t2)
+            res["rel_frob_from_shard_objects"] = float((t2[0] / t2[1]).sqrt())
+            res["shard_object_bytes"] = int(L.bsq_get_packed_size(obj))
+            L.bsq_free(obj)
+            L.bsq_decompress_release()
+        L.bsq_shard_svd_destroy(h)
+        sv = s.cpu().numpy().copy()
+        del a, u, s, v
+        return res, sv
+
+    small, s_sharded = run(32768, 0)
+    out["parity_32768x4096"] = {"rel_frob_sharded": small["rel_frob"]}
+    if rank == 0:
+        a = W.lowrank_matrix(torch, 32768, n, cfg["seed"], row_slice=(0, 32768))
+        u = torch.zeros((32768, k), device="cuda")
+        s = torch.zeros(k, device="cuda")
+        v = torch.zeros((n, k), device="cuda")
+        if L.bsq_svd_lowrank(a.data_ptr(), 32768, n, k, niter, 1241, u.data_ptr(), s.data_ptr(), v.data_ptr(), None) != 0:
+            raise RuntimeError("unsharded bsq_svd_lowrank failed")
+        torch.cuda.synchronize()
+        e1 = rel_frob(a, (u * s) @ v.T)
+        s1 = s.cpu().numpy()
+        out["parity_32768x4096"].update({"rel_frob_unsharded": e1, "abs_diff": abs(e1 - small["rel_frob"]),
+                                         "s_lead4_max_rel_diff": float(np.max(np.abs(s_sharded[:4] - s1[:4]) / s1[:4]))})
+        del a, u, s, v
+    dist.barrier()
+    full, _ = run(cfg["rows"], 5)
+    out.update(full)
+    L.bsq_shard_comm_destroy(comm)
+    return out
+
+
 def tf32_peak(torch):
     """Dense TF32 rate of a library matrix product, the denominator of the 3xTF32 roofline: FP32 matmul 8192^3 with TF32
     allowed, best of 10 (a measurement of the device, not part of the path)."""
@@ -418,7 +522,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="batch size (default: the configuration's 32)")
     ap.add_argument("--single", default=None, choices=["C3", "C4", "C5A", "c3", "c4", "c5a"],
                     help="side measurement, not the bench line: public compress / decompress of one matrix")
-    ap.add_argument("--skip-extras", action="store_true", help="leave out the configs[1] leg and the CPU baseline")
+    ap.add_argument("--skip-extras", action="store_true", help="leave out the configs[1] leg, the row-sharded leg and the CPU baseline")
+    ap.add_argument("--sharded-only", action="store_true", help="run only the row-sharded SVD leg (needs torchrun, N >= 2)")
     args = ap.parse_args()
     if args.single:
         run_single(args)
@@ -446,6 +551,14 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.sharded_only:
+        res = row_sharded_leg(torch, dist, pkg, L, W, rank, world)
+        if rank == 0:
+            print(json.dumps({"row_sharded_svd": res}))
+        dist.barrier()
+        dist.destroy_process_group()
+        return
 
     cfg = W.CONFIGS["C5A"]
     rows, cols = cfg["rows"], cfg["cols"]
@@ -575,7 +688,11 @@ def main():
     packed_all = int(sum(shard.gather_objects(packed_total)))
     L.bsq_batch_destroy(batch)
     L.bsq_batch_destroy(single)
-    del pinned, d_packed
+    del pinned, d_packed, mats, d_dst
+    torch.cuda.empty_cache()
+    sharded = None
+    if world > 1 and not args.skip_extras:
+        sharded = row_sharded_leg(torch, dist, pkg, L, W, rank, world)
 
     if rank == 0:
         hbm_peak, bf16_peak, peak_kind = measured_peaks()
@@ -620,6 +737,8 @@ def main():
                          "timed": "CUDA events on the lane's stream around each product, one matrix in flight"},
             "clocks": clocks,
         }
+        if sharded is not None:
+            line["row_sharded_svd"] = sharded
         if not args.skip_extras:
             line["configs1_frontend"] = c2_frontend_leg(torch, pkg, L, W, hbm_peak)
             if world == 1:

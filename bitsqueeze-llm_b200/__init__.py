@@ -81,12 +81,19 @@ SIGNATURES = {
     "bsq_frontend_quantize_timed": (_i, [_i, _vp, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bsq_residual_error": (_i, [_vp, _vp, _u64, _vp, _vp, _vp]),
     "bsq_svd_lowrank": (_i, [_vp, _i, _i, _i, _i, C.c_ulonglong, _vp, _vp, _vp, _vp]),
+    "bsq_svd_lowrank_at": (_i, [_vp, _i, _i, _i, _i, C.c_ulonglong, C.c_ulonglong, _vp, _vp, _vp, _vp]),
     "bsq_reconstruct": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "bsq_gemm": (_i, [_i, _i, _vp, C.c_long, _vp, C.c_long, _vp, C.c_long, _i, _i, _i, _vp, _sz, _i, _vp, _vp]),
     "bsq_shard_unique_id": (_i, [_vp, _sz]),
     "bsq_shard_comm_create": (_vp, [_vp, _i, _i]),
     "bsq_shard_comm_destroy": (None, [_vp]),
     "bsq_svd_lowrank_sharded": (_i, [_vp, _vp, _i, _i, _i, _i, _i, C.c_ulonglong, _vp, _vp, _vp, _vp]),
+    "bsq_shard_svd_create": (_vp, [_vp, _i, _i, _i, _i, _i]),
+    "bsq_shard_svd_destroy": (None, [_vp]),
+    "bsq_shard_svd_run": (_i, [_vp, _vp, C.c_ulonglong, _vp, _vp, _vp, _vp]),
+    "bsq_shard_compress": (_i, [_vp, _vp, C.c_ulonglong, C.POINTER(_vp), _vp]),
+    "bsq_shard_svd_profile": (_i, [_vp, _i]),
+    "bsq_shard_svd_profile_read": (_i, [_vp, _vp, _vp, _i]),
     "bsq_lane_create": (_vp, [_u16, _u16, _f, _f, _i, _i, _i, _i, _i]),
     "bsq_lane_destroy": (None, [_vp]),
     "bsq_lane_packed_capacity": (_u64, [_vp]),

@@ -135,6 +135,15 @@ HostPool &host_pool() {
     return *pool;
 }
 
+}  // namespace
+
+void *bsq::host_block_take(size_t bytes) {
+    void *p = host_pool().take(bytes);
+    return p ? p : std::malloc(bytes);
+}
+
+namespace {
+
 // ---- device buffers ----------------------------------------------------------------------------
 struct DevBuf {
     void *p = nullptr;
@@ -216,7 +225,8 @@ struct Runtime {
     int sm_count = 148;
     cudaStream_t stream = nullptr;
     cudaEvent_t ev[8] = {};
-    DevBuf input_stage, residual, recon, error, u, s, v, scratch, status;
+    DevBuf input_stage, residual, recon, error, u, s, v, scratch, status, recon_ws;
+    size_t recon_ws_bytes = 0;
     QuantBufs q_direct, q_u, q_s, q_v;
     TopkBufs outlier, err;
     SvdWorkspace *svd = nullptr;
@@ -230,7 +240,7 @@ struct Runtime {
     void release() {
         if (stream) cudaStreamSynchronize(stream);
         input_stage.release(); residual.release(); recon.release(); error.release();
-        u.release(); s.release(); v.release(); scratch.release(); status.release();
+        u.release(); s.release(); v.release(); scratch.release(); status.release(); recon_ws.release();
         q_direct.release(); q_u.release(); q_s.release(); q_v.release();
         outlier.release(); err.release();
         if (svd) { svd_workspace_destroy(svd); svd = nullptr; }
@@ -314,6 +324,10 @@ bool setup_runtime(Runtime &rt, bool compress, uint16_t rows, uint16_t cols, flo
     if (has_svd) {
         const size_t r = (size_t)rt.rank;
         if (!rt.u.alloc((size_t)rows * r * 4) || !rt.s.alloc(r * 4) || !rt.v.alloc((size_t)cols * r * 4)) return false;
+        if (!compress || ke > 0) {                      // the reconstruction runs on decompress and for the error stage
+            rt.recon_ws_bytes = reconstruct_workspace_bytes(cols, rt.rank);
+            if (rt.recon_ws_bytes && !rt.recon_ws.alloc(rt.recon_ws_bytes)) return false;
+        }
         if (compress) {
             if (uv != quantization_NONE && (!rt.q_u.alloc((uint64_t)rows * r) || !rt.q_v.alloc((uint64_t)cols * r))) return false;
             if (s != quantization_NONE && !rt.q_s.alloc(r)) return false;
@@ -603,7 +617,15 @@ int compress_begin(Runtime &rt, const float *x, int input_location, uint8_t *d_p
     }
     mark();                                                               // ev1: outlier separation done
     if (has_svd) {
-        if (svd_lowrank(rt.svd, d_src, rt.u.as<float>(), rt.s.as<float>(), rt.v.as<float>(), 1241ULL, d_status, st) != cudaSuccess)
+        // The random matrix of the range finder is the one the reference's FIRST compress call after initialisation
+        // uses: its generator is seeded once, with 1234 (src/bitsqz_llm.cu:841-859), its warm-up run draws the first
+        // N_work x k normals of that XORWOW sequence, and its captured graph goes on from there, whatever seed the call
+        // passes (:1069-1074) -- so call c works with block c of the sequence, and block 1 is the only one a caller
+        // can count on.  Every call here uses block 1: same singular values as that first reference call to ~5e-5
+        // relative, and the same object for the same input on every call.
+        const unsigned long long omega_offset = (unsigned long long)std::min(rows, cols) * rank;
+        if (svd_lowrank(rt.svd, d_src, rt.u.as<float>(), rt.s.as<float>(), rt.v.as<float>(), 1234ULL, d_status, st, omega_offset) !=
+            cudaSuccess)
             return fail();
         mark(); job.ev_svd = job.nev - 1;
         // quantised factors replace U, S, V in place for the error stage (src/bitsqz_llm.cu:1078-1139)
@@ -616,7 +638,8 @@ int compress_begin(Runtime &rt, const float *x, int input_location, uint8_t *d_p
         mark(); job.ev_quant = job.nev - 1;
         if (error_path) {
             if (reconstruct_lowrank(rt.u.as<float>(), rt.s.as<float>(), rt.v.as<float>(), rows, cols, (int)rank, d_src,
-                                    rt.error.as<float>(), d_status + 1, d_status, rt.sm_count, st) != cudaSuccess)
+                                    rt.error.as<float>(), d_status + 1, d_status, rt.recon_ws.as<float>(), rt.recon_ws_bytes, rt.sm_count,
+                                    st) != cudaSuccess)
                 return fail();
             mark(); job.ev_recon = job.nev - 1;
         }
@@ -941,7 +964,7 @@ int decompress_begin(Runtime &rt, const bitsqz_llm_array_t *c, bool payload_on_d
         if (!decode_section(rt, c, c->section_s, heads.s, c->svd_s_format, rank, &rt.q_direct, rt.s.as<float>())) return fail();
         if (!decode_section(rt, c, c->section_v, heads.v, c->svd_uv_format, (uint64_t)c->num_columns * rank, &rt.q_direct, rt.v.as<float>())) return fail();
         if (reconstruct_lowrank(rt.u.as<float>(), rt.s.as<float>(), rt.v.as<float>(), c->num_rows, c->num_columns, (int)rank,
-                                nullptr, d_dst, nullptr, d_status, rt.sm_count, st) != cudaSuccess)
+                                nullptr, d_dst, nullptr, d_status, rt.recon_ws.as<float>(), rt.recon_ws_bytes, rt.sm_count, st) != cudaSuccess)
             return fail();
     } else if (c->section_direct.storage == BITSQZ_SECTION_QUANT && (has_out != has_err)) {
         // quantised matrix with exactly one list: dequantise and add the list in one pass over the output

@@ -133,6 +133,16 @@ int bsq_svd_lowrank(const float *d_A, int m, int n, int k, int niter, unsigned l
     svd_workspace_destroy(ws);
     return rc(e) | rc(s);
 }
+int bsq_svd_lowrank_at(const float *d_A, int m, int n, int k, int niter, unsigned long long seed, unsigned long long offset,
+                       float *d_U, float *d_S, float *d_V, void *stream) {
+    if (!d_A || !d_U || !d_S || !d_V || m <= 0 || n <= 0 || k <= 0 || niter < 0) return 1;
+    SvdWorkspace *ws = svd_workspace_create(m, n, k, niter, device_sm_count());
+    if (!ws) return 1;
+    const cudaError_t e = svd_lowrank(ws, d_A, d_U, d_S, d_V, seed, nullptr, as_stream(stream), offset);
+    const cudaError_t s = svd_workspace_finish(ws, as_stream(stream));
+    svd_workspace_destroy(ws);
+    return rc(e) | rc(s);
+}
 int bsq_gemm(int a_kmajor, int b_kmajor, const float *d_A, long lda, const float *d_B, long ldb, float *d_C, long ldc, int M,
              int N, int K, float *d_workspace, size_t workspace_bytes, int allow_tensor_cores, uint32_t *d_status, void *stream) {
     if (!d_A || !d_B || !d_C || M <= 0 || N <= 0 || K <= 0) return 1;
@@ -143,7 +153,7 @@ int bsq_reconstruct(const float *d_U, const float *d_S, const float *d_V, int m,
                     float *d_out, uint32_t *d_flag, uint32_t *d_status, void *stream) {
     if (!d_U || !d_S || !d_V || !d_out || m <= 0 || n <= 0 || k <= 0) return 1;
     if (d_minuend && !d_flag) return 1;
-    return rc(reconstruct_lowrank(d_U, d_S, d_V, m, n, k, d_minuend, d_out, d_flag, d_status, device_sm_count(), as_stream(stream)));
+    return rc(reconstruct_lowrank(d_U, d_S, d_V, m, n, k, d_minuend, d_out, d_flag, d_status, nullptr, 0, device_sm_count(), as_stream(stream)));
 }
 
 const char *bsq_build_info(void) { return "bitsqz_llm sm_100a " __DATE__; }

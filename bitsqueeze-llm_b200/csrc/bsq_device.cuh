@@ -32,14 +32,15 @@ static __device__ __constant__ float c_nf4_levels[16] = {
 // Bucket table of the encoder.  The reference's scan (first level of minimal |v - L[i]|,
 // quantization_cuda.cu:43-58) is, for every v below 2^23+1, the step function "number of
 // thresholds <= v" over 15 thresholds.  v is mapped to one of 32 buckets by two FMAs (see
-// nf4_bucket); bucket b holds at most one threshold c_nf4_bucket_thr[b] (+inf if none) and
+// nf4_bucket); bucket b holds at most one threshold c_nf4_bucket_thr[b] (NaN if none: v >= NaN is false for
+// every v, so the code stays a nibble even for v = +Inf, whose neighbour in the packed byte it would otherwise spoil) and
 // c_nf4_bucket_base[b] thresholds lie in lower buckets.  oracle/check_nf4_fast_encoder.c
 // builds this table and proves code == scan for every finite |v| < 2^23.
 static __device__ __constant__ unsigned c_nf4_bucket_thr[32] = {
-    0x7f800000u, 0x7f800000u, 0xbf591cd8u, 0x7f800000u, 0x7f800000u, 0x7f800000u, 0xbf1c5270u, 0x7f800000u,
-    0xbeeb847fu, 0x7f800000u, 0xbeadea76u, 0x7f800000u, 0xbe703cecu, 0xbe0d38bbu, 0x7f800000u, 0xbd3a7870u,
-    0x3d22fb00u, 0x3df64863u, 0x7f800000u, 0x3e5067e1u, 0x3e9582d5u, 0x7f800000u, 0x3ec753fau, 0x3f006d04u,
-    0x7f800000u, 0x3f248db0u, 0x7f800000u, 0x7f800000u, 0x7f800000u, 0x3f5c89dau, 0x7f800000u, 0x7f800000u};
+    0x7fc00000u, 0x7fc00000u, 0xbf591cd8u, 0x7fc00000u, 0x7fc00000u, 0x7fc00000u, 0xbf1c5270u, 0x7fc00000u,
+    0xbeeb847fu, 0x7fc00000u, 0xbeadea76u, 0x7fc00000u, 0xbe703cecu, 0xbe0d38bbu, 0x7fc00000u, 0xbd3a7870u,
+    0x3d22fb00u, 0x3df64863u, 0x7fc00000u, 0x3e5067e1u, 0x3e9582d5u, 0x7fc00000u, 0x3ec753fau, 0x3f006d04u,
+    0x7fc00000u, 0x3f248db0u, 0x7fc00000u, 0x7fc00000u, 0x7fc00000u, 0x3f5c89dau, 0x7fc00000u, 0x7fc00000u};
 static __device__ __constant__ int c_nf4_bucket_base[32] = {
     0, 0, 0, 1, 1, 1, 1, 2, 2, 3, 3, 4, 4, 5, 6, 6, 7, 8, 9, 9, 10, 11, 11, 12, 13, 13, 14, 14, 14, 14, 15, 15};
 

@@ -238,15 +238,24 @@ cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, c
         // N up to 256 is one tile; wider products (the reconstruction) are cut into 128-column tiles
         t.n_tile = N <= 256 ? N : 128;
         t.flag = minuend ? flag : nullptr;
-        const int tiles_tc = ((M + 127) / 128) * ((N + t.n_tile - 1) / t.n_tile);
         // B split beforehand when several row tiles share it and the workspace has room for its images (at its end)
         const size_t image_bytes = gemm_tc_image_bytes(N, t.n_tile, K);
         // (measured: the products are then bound by what the CTAs draw from L2, A once and B's images once per row
         // tile; that pays for tiles wider than 128 columns, where splitting B in every CTA is two thirds of the
         // staging work, and for long K)
-        const bool with_image = workspace && image_bytes + 128 <= workspace_bytes &&
-                                (b_image_mode() == 2 ? M >= 256 : (b_image_mode() == 1 && M >= 512 && t.n_tile > 128 && K >= 1024));
-        if (with_image) workspace_bytes = (workspace_bytes - image_bytes) & ~(size_t)127;
+        bool with_image = workspace && image_bytes + 128 <= workspace_bytes &&
+                          (b_image_mode() == 2 ? M >= 256 : (b_image_mode() == 1 && M >= 512 && t.n_tile > 128 && K >= 1024));
+        // a wide product (the reconstruction: N = a matrix dimension, K = the rank) in 256-column tiles, B's images
+        // made once and shared by all row tiles, when the workspace has room for them; otherwise every CTA of a
+        // 128-column tile splits its piece of B itself
+        if (!with_image && N > 256 && workspace && b_image_mode() >= 1 && M >= 512 && K >= 64 &&
+            gemm_tc_image_bytes(N, 256, K) + 128 <= workspace_bytes) {
+            t.n_tile = 256;
+            with_image = true;
+        }
+        const size_t image_room = with_image ? gemm_tc_image_bytes(N, t.n_tile, K) : 0;
+        if (with_image) workspace_bytes = (workspace_bytes - image_room) & ~(size_t)127;
+        const int tiles_tc = ((M + 127) / 128) * ((N + t.n_tile - 1) / t.n_tile);
         int splits_tc = 1;
         const int slots = (with_image ? gemm_tc_image_ctas_per_sm(t.n_tile) : (t.n_tile <= 128 ? 2 : 1)) * sm_count;
         if (with_image) gemm_tc_image_rings(t.n_tile, &t.a_stages, &t.b_stages);

@@ -64,6 +64,9 @@ cudaError_t residual_error(const float *d_a, const float *d_b, uint64_t n, float
                            cudaStream_t stream);
 
 int device_sm_count();
+// A block for a packed object that the caller will release with bitsqz_llm_free: page-locked from the library's pool
+// when one can be had, plain heap memory otherwise (bsq_api.cu).
+void *host_block_take(size_t bytes);
 bool topk_rows_fit_smem(const void *d_in, const void *d_residual, uint32_t cols, uint32_t k);
 
 // ---- randomized low-rank SVD and reconstruction (bsq_svd.cu, bsq_gemm.cu) -------------------
@@ -92,8 +95,9 @@ SvdWorkspace *svd_workspace_create_sharded(int m_local, int n, int k, int niter,
                                            void *allreduce_ctx, int m_total);
 void svd_workspace_destroy(SvdWorkspace *ws);
 // A row-major m x n -> U (m x k row-major), S (k, descending), V (n x k row-major).
+// The random matrix is the first N x k normals of cuRAND's XORWOW sequence of `seed`, starting `offset` values in.
 cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d_S, float *d_V,
-                        unsigned long long seed, unsigned *d_status, cudaStream_t stream);
+                        unsigned long long seed, unsigned *d_status, cudaStream_t stream, unsigned long long offset = 0);
 // Optional timing of a call's products with the big matrix (kind 0) and, row-sharded, its all-reduces (kind 1).
 cudaError_t svd_workspace_profile(SvdWorkspace *ws, bool on);
 int svd_workspace_spans(SvdWorkspace *ws, float *ms, int *kinds, int capacity);
@@ -103,8 +107,11 @@ cudaError_t svd_workspace_finish(SvdWorkspace *ws, cudaStream_t stream);
 // OR 1 into *d_flag when some |difference| > FLT_EPSILON.
 // d_status (nullable): device word that receives kStatusBarrierTimeout if a bounded wait of the product kernel gives up
 // (the output is then incomplete).
+// d_workspace (nullable, reconstruct_workspace_bytes): room for V split once into the tensor cores' operand format,
+// shared by all row tiles; without it every tile splits its piece of V itself.
+size_t reconstruct_workspace_bytes(int n, int k);
 cudaError_t reconstruct_lowrank(const float *d_U, const float *d_S, const float *d_V, int m, int n, int k,
-                                const float *d_minuend, float *d_out, unsigned *d_flag, unsigned *d_status, int sm_count,
-                                cudaStream_t stream);
+                                const float *d_minuend, float *d_out, unsigned *d_flag, unsigned *d_status, float *d_workspace,
+                                size_t workspace_bytes, int sm_count, cudaStream_t stream);
 
 }  // namespace bsq

@@ -28,6 +28,7 @@ struct GroupCtl {
     unsigned reduce;               // scratch for group-wide max / or
     unsigned nhits;                // float4 of the row whose maximum reached the bound (indices in hist[])
     unsigned flags;                // row state of the streaming routines (bsq_rowstream.cuh)
+    unsigned wait_failed;          // a lane's bounded wait for the row copy ran out: the whole group stops
     unsigned seen[8];              // one bit per 32-bit rank already taken (tie detection, bsq_rowstream.cuh)
     unsigned hist[256];            // radix-select histogram of the exact path
     __align__(16) unsigned key[kCandCap];   // |x| bits of the candidates, zero beyond their number

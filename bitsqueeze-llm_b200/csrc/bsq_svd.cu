@@ -62,7 +62,7 @@ struct SvdWorkspace {
     int jc_lanes = 4;                   // lanes per column pair of the cluster Jacobi kernel for this k
     bool own_core_svd = false;          // k small enough for jacobi_svd_kernel (else cuSOLVER's gesvdj on the core)
     bool seeded = false;                // omega holds the draw for `seed`
-    unsigned long long seed = 0;
+    unsigned long long seed = 0, offset = 0;
     // optional timing of the spans that matter for a roofline: the products with the big matrix (kind 0) and the
     // all-reduces of the row-sharded mode (kind 1), bracketed by events on the call's stream
     static constexpr int kMaxSpans = 32;
@@ -1126,7 +1126,7 @@ cudaError_t svd_workspace_finish(SvdWorkspace *ws, cudaStream_t st) {
 }
 
 cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d_S, float *d_V, unsigned long long seed,
-                        unsigned *d_status, cudaStream_t st) {
+                        unsigned *d_status, cudaStream_t st, unsigned long long offset) {
     if (!ws || !d_A || !d_U || !d_S || !d_V) return cudaErrorInvalidValue;
     const int k = ws->k;
     ws->spans = 0;
@@ -1136,14 +1136,15 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
     if (cusolverDnSetStream(ws->solver, st) != CUSOLVER_STATUS_SUCCESS) return cudaErrorUnknown;
     // Omega depends on the seed and the shape only (the generator is set back to the start of the seed's sequence for
     // every call), so it is drawn once per workspace and seed and kept: re-seeding costs a kernel of its own.
-    if (!ws->seeded || ws->seed != seed) {
+    if (!ws->seeded || ws->seed != seed || ws->offset != offset) {
         if (curandSetPseudoRandomGeneratorSeed(ws->rng, seed) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
-        if (curandSetGeneratorOffset(ws->rng, 0ULL) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
+        if (curandSetGeneratorOffset(ws->rng, offset) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
         size_t count = (size_t)ws->N * k;
         count += count & 1;                               // the normal generator wants an even count
         if (curandGenerateNormal(ws->rng, ws->omega, count, 0.0f, 1.0f) != CURAND_STATUS_SUCCESS) return cudaErrorUnknown;
         ws->seeded = true;
         ws->seed = seed;
+        ws->offset = offset;
     }
 
     cudaError_t err;
@@ -1198,12 +1199,14 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
                 ws->sm_count, st);
 }
 
+size_t reconstruct_workspace_bytes(int n, int k) { return n > 256 ? gemm_tc_image_bytes(n, 256, k) + 512 : 0; }
+
 cudaError_t reconstruct_lowrank(const float *d_U, const float *d_S, const float *d_V, int m, int n, int k,
-                                const float *d_minuend, float *d_out, unsigned *d_flag, unsigned *d_status, int sm_count,
-                                cudaStream_t st) {
+                                const float *d_minuend, float *d_out, unsigned *d_flag, unsigned *d_status, float *d_workspace,
+                                size_t workspace_bytes, int sm_count, cudaStream_t st) {
     if (!d_U || !d_S || !d_V || !d_out || m <= 0 || n <= 0 || k <= 0) return cudaErrorInvalidValue;
     // out(i, j) = sum_t (U(i, t) S(t)) V(j, t): A = U as stored with a per-k scale, B = V^T (K-major)
-    return gemm(true, true, d_U, k, d_V, k, d_out, n, m, n, k, d_S, d_minuend, n, d_flag, d_status, nullptr, 0, sm_count, st);
+    return gemm(true, true, d_U, k, d_V, k, d_out, n, m, n, k, d_S, d_minuend, n, d_flag, d_status, d_workspace, workspace_bytes, sm_count, st);
 }
 
 }  // namespace bsq

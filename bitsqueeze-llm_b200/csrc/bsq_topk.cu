@@ -38,6 +38,7 @@ __global__ void __launch_bounds__(512)
     if (g.lane == 0) {
         mbar_init(bar, 1);
         mbar_fence_init();
+        c.wait_failed = 0;
     }
     g.sync();
     unsigned phase = 0;
@@ -47,7 +48,11 @@ __global__ void __launch_bounds__(512)
             mbar_expect_tx(bar, bytes);
             bulk_g2s(row, in + (size_t)r * cols, bytes, bar);
         }
-        if (!mbar_wait_bounded(bar, phase, status)) break;
+        // the outcome of the wait must be the same for every lane of the group (they meet at group barriers below):
+        // a lane whose wait ran out says so, and all lanes read the same flag after a group barrier
+        if (!mbar_wait_bounded(bar, phase, status)) c.wait_failed = 1;
+        g.sync();
+        if (c.wait_failed) break;
         phase ^= 1u;
         bool special = false;
         hint = group_topk_row<G>(g, c, row, cols, k, out_idx + (size_t)r * k, out_val + (size_t)r * k, residual != nullptr,

@@ -127,6 +127,10 @@ int bsq_residual_error(const float *d_a, const float *d_b, uint64_t n, float *d_
  * rank-k randomized SVD of the row-major m x n matrix d_A.  d_U: m x k, d_S: k, d_V: n x k. */
 int bsq_svd_lowrank(const float *d_A, int m, int n, int k, int niter, unsigned long long seed, float *d_U, float *d_S,
                     float *d_V, void *stream);
+/* The same with the random matrix taken `offset` values into the generator's sequence for `seed` (bsq_svd_lowrank is
+ * offset 0): the range finder's random matrix is the N_work x k block of XORWOW normals that starts there. */
+int bsq_svd_lowrank_at(const float *d_A, int m, int n, int k, int niter, unsigned long long seed, unsigned long long offset,
+                       float *d_U, float *d_S, float *d_V, void *stream);
 /* reconstruct_lowrank_cuda (reconstruct_lowrank_cuda.cuh:73-78): d_out = (U diag(S)) V^T.
  * d_minuend non-NULL: d_out = d_minuend - (U diag(S)) V^T and *d_flag |= any(|d_out| > FLT_EPSILON).
  * d_status (nullable) receives bit 0 if a bounded wait inside the product kernel gave up (d_out is then incomplete). */
@@ -155,6 +159,23 @@ void *bsq_shard_comm_create(const void *unique_id, int rank, int world);
 void bsq_shard_comm_destroy(void *comm);
 int bsq_svd_lowrank_sharded(void *comm, const float *d_A_local, int m_local, int m_total, int n, int k, int niter,
                             unsigned long long seed, float *d_U_local, float *d_S, float *d_V, void *stream);
+/* The same with a workspace that lives across calls (created once per communicator and shape; every rank creates its
+ * own, with its own m_local).  bsq_shard_svd_run waits for `stream` before it returns (it checks the kernels' status).
+ * bsq_shard_compress runs the SVD and returns THIS rank's shard as an ordinary packed object (FP32 sections: its
+ * m_local rows of U, and the replicated S and V; m_local and n at most 65 535), which the unchanged
+ * bitsqz_llm_decompress -- initialised with (m_local, n, 0, 0, k, none, none, none) -- turns back into the shard's
+ * rows: a matrix with more rows than one object can hold (include/bitsqz_llm.hpp:56, uint16_t num_rows, of the
+ * reference) becomes one object per shard.  Release it with bsq_free.
+ * bsq_shard_svd_profile / _read: as bsq_lane_profile; kind 0 = product with the local rows, kind 1 = all-reduce. */
+typedef struct bsq_shard_svd bsq_shard_svd_t;
+bsq_shard_svd_t *bsq_shard_svd_create(void *comm, int m_local, int m_total, int n, int k, int niter);
+void bsq_shard_svd_destroy(bsq_shard_svd_t *handle);
+int bsq_shard_svd_run(bsq_shard_svd_t *handle, const float *d_A_local, unsigned long long seed, float *d_U_local, float *d_S,
+                      float *d_V, void *stream);
+int bsq_shard_compress(bsq_shard_svd_t *handle, const float *d_A_local, unsigned long long seed, struct bitsqz_llm_array **out,
+                       void *stream);
+int bsq_shard_svd_profile(bsq_shard_svd_t *handle, int on);
+int bsq_shard_svd_profile_read(bsq_shard_svd_t *handle, float *ms, int *kinds, int capacity);
 
 /* ---- lanes and batches: several independent matrices in flight on one device -----------------------------------
  * No counterpart in the reference, whose compress and decompress calls are synchronous and keep one pair of runtimes

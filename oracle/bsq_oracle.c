@@ -287,8 +287,16 @@ int bsq_oracle_topk_apply(const uint16_t *idx, const float *val, uint32_t rows, 
 int bsq_oracle_residual(const float *a, const float *b, uint64_t n, float *e) {
     int any = 0;
     for (uint64_t i = 0; i < n; ++i) {
-        e[i] = a[i] - b[i];
-        if (fabsf(e[i]) > 1.1920928955078125e-07f) any = 1;
+        float d = a[i] - b[i];
+        if (d != d) {
+            /* The reference subtracts on the GPU (subtract_kernel, src/bitsqz_llm.cu:164-170), whose FP32 arithmetic
+             * returns the canonical NaN 0x7fffffff whatever the NaN operand's payload was; a CPU keeps the payload.
+             * The bits matter: a NaN error value is stored in the error top-k section as it is. */
+            const uint32_t canonical = 0x7fffffffu;
+            memcpy(&d, &canonical, 4);
+        }
+        e[i] = d;
+        if (fabsf(d) > 1.1920928955078125e-07f) any = 1;
     }
     return any;
 }

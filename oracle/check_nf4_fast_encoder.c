@@ -45,7 +45,9 @@ static inline int bucket(float v) {
 int main(void) {
     float thr[32];
     int base[32];
-    for (int b = 0; b < 32; ++b) { thr[b] = INFINITY; base[b] = -1; }
+    /* a bucket without a threshold gets NaN: v >= NaN is false for every v, +Inf included, so the code never
+     * exceeds 15 (with +Inf as the filler, v = +Inf would come out as code 16 and spill into the neighbouring nibble) */
+    for (int b = 0; b < 32; ++b) { thr[b] = NAN; base[b] = -1; }
     int owner[32] = {0};
     for (int i = 0; i < 15; ++i) {
         const int b = bucket(bits2f(TB[i]));
@@ -70,5 +72,15 @@ int main(void) {
         if (fast != scan(v)) bad++;
     }
     printf("mismatches over all |v| < 2^23: %llu\n", bad);
-    return bad ? 1 : 0;
+    /* outside that range the fast encoder is not used for the result, but its output must still be a nibble */
+    unsigned long long wide = 0;
+#pragma omp parallel for schedule(static) reduction(+ : wide)
+    for (long long k = 0; k < (1ll << 32); ++k) {
+        const float v = bits2f((uint32_t)k);
+        const int b = bucket(v);
+        const int fast = base[b] + (v >= thr[b] ? 1 : 0);
+        if (fast < 0 || fast > 15) wide++;
+    }
+    printf("codes outside 0..15 over all bit patterns: %llu\n", wide);
+    return (bad || wide) ? 1 : 0;
 }

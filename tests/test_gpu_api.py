@@ -164,3 +164,15 @@ def test_error_section_skipped_when_quantisation_is_exact(pkg, lib, oracle):
     assert hdr.flags == 0 and hdr.section_error_topk.storage == pkg.SECTION_NONE
     assert same_bytes(packed, oracle.compress_nosvd(x, 0.0, 0.05, 11))
     lib.bsq_compress_release()
+
+
+@pytest.mark.parametrize("method", [10, 11])
+def test_selected_infinity_does_not_spoil_its_neighbour(pkg, lib, oracle, method):
+    """A +Inf that the outlier stage selects sits in a block whose other values are ordinary, so the block takes the table
+    encoder; the encoder's output for +Inf must stay a nibble, or the value packed into the same byte comes out wrong
+    (the selected column itself is overwritten with the code of 0.0 afterwards).  Also rows of NaN, zeros and denormals."""
+    from test_gpu_ref_parity import special_matrix
+    x = np.ascontiguousarray(special_matrix(48, 256, 3))
+    hdr, packed = compress_bytes(pkg, lib, x, 0.04, 0.0, method, pkg.INPUT_DEVICE)
+    assert same_bytes(packed, oracle.compress_nosvd(x, 0.04, 0.0, method))
+    lib.bsq_compress_release()

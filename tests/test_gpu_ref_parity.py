@@ -203,8 +203,9 @@ def test_svd_configuration_shapes_against_reference_cuda(pkg, lib, ref, workload
             # the same object through both decompressors: FP32 products in a different summation order
             assert rel_frob_t(y_own, d_y) <= 1e-5
     ref.lib.ref_decompress_release()
-    # the contract: reconstruction error within 1e-4 (absolute, on the relative Frobenius error) of the reference's
-    assert abs(y["ours/ours"] - y["theirs/theirs"]) <= 1e-4, y
+    # the contract: reconstruction error within 1e-4 (absolute, on the relative Frobenius error) of the reference's;
+    # with the same random matrix the two agree far better than that
+    assert abs(y["ours/ours"] - y["theirs/theirs"]) <= 2e-5, y
     assert abs(y["ours/theirs"] - y["theirs/theirs"]) <= 1e-5 and abs(y["theirs/ours"] - y["ours/ours"]) <= 1e-5, y
 
     if cfg["uv"] == -1 and cfg["s"] == -1:
@@ -215,18 +216,16 @@ def test_svd_configuration_shapes_against_reference_cuda(pkg, lib, ref, workload
         assert np.abs(u.astype(np.float64).T @ u - eye).max() <= 1e-4
         assert np.abs(v.astype(np.float64).T @ v - eye).max() <= 1e-4
         assert np.all(np.diff(s) <= 1e-6 * s[0])
-        # Singular values.  Both libraries sketch the same matrix with a rank-k random range finder and no oversampling,
-        # so each one's values fall short of the exact ones by an amount that depends on its random matrix; the
-        # reference's own values move by that much between two calls on the same input.  What both must agree on to
-        # 1e-4 relative is everything the sketch resolves: the energy they capture (the sum of squares) and the
-        # well-separated leading values.
+        # Singular values: all of them to 1e-4 relative against the reference's first call after initialisation, the one
+        # call whose random matrix its seeds define (block 1 of the XORWOW sequence of seed 1234, which this library
+        # uses for every call).  Measured: 4.4e-5 at this shape.
+        assert np.max(np.abs(s - rs) / rs) <= 1e-4, float(np.max(np.abs(s - rs) / rs))
+        # against the exact values both fall short by the same few per cent (a rank-k sketch without oversampling of a
+        # spectrum that is nearly flat at k), and both stay below them
         exact = torch.linalg.svdvals(a.double()).cpu().numpy()[:rank]
-        assert abs(np.sum(s.astype(np.float64) ** 2) - np.sum(rs.astype(np.float64) ** 2)) / np.sum(rs.astype(np.float64) ** 2) <= 1e-4
-        lead = 4
-        assert np.max(np.abs(s[:lead] - rs[:lead]) / rs[:lead]) <= 1e-4, (s[:lead], rs[:lead])
-        assert np.max(np.abs(s[:lead] - exact[:lead]) / exact[:lead]) <= 1e-4
-        # over the whole range both stay below the exact values and within the same distance of them
         assert np.all(s <= exact * (1 + 1e-4)) and np.all(rs <= exact * (1 + 1e-4))
-        dev_ours = np.max((exact - s) / exact)
-        dev_ref = np.max((exact - rs) / exact)
-        assert dev_ours <= dev_ref * 1.25 + 1e-4, (dev_ours, dev_ref)
+        assert abs(np.max((exact - s) / exact) - np.max((exact - rs) / exact)) <= 1e-4
+        # same subspaces: the leading left and right singular vectors agree up to sign
+        for f_ours, f_ref in ((u, ru), (v, rv)):
+            cosines = np.abs(np.sum(f_ours[:, :4].astype(np.float64) * f_ref[:, :4], axis=0))
+            assert np.all(cosines >= 1 - 1e-3), cosines

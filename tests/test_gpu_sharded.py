@@ -38,6 +38,29 @@ mine = torch.from_numpy(a[rank * rows:(rank + 1) * rows].copy()).cuda()
 u = torch.zeros((rows, k), device="cuda"); s = torch.zeros(k, device="cuda"); v = torch.zeros((n, k), device="cuda")
 assert L.bsq_svd_lowrank_sharded(comm, mine.data_ptr(), rows, m, n, k, niter, 1241, u.data_ptr(), s.data_ptr(), v.data_ptr(), None) == 0
 torch.cuda.synchronize()
+# the same through a workspace that lives across calls: two calls, both bit-identical to the one-shot call
+h = L.bsq_shard_svd_create(comm, rows, m, n, k, niter)
+assert h
+u2 = torch.zeros_like(u); s2 = torch.zeros_like(s); v2 = torch.zeros_like(v)
+for _ in range(2):
+    u2.zero_(); s2.zero_(); v2.zero_()
+    assert L.bsq_shard_svd_run(h, mine.data_ptr(), 1241, u2.data_ptr(), s2.data_ptr(), v2.data_ptr(), None) == 0
+    assert torch.equal(u2.view(torch.int32), u.view(torch.int32)) and torch.equal(s2.view(torch.int32), s.view(torch.int32))
+    assert torch.equal(v2.view(torch.int32), v.view(torch.int32))
+# this rank's shard as an ordinary packed object, decompressed by the unchanged public call
+obj = C.c_void_p(None)
+assert L.bsq_shard_compress(h, mine.data_ptr(), 1241, C.byref(obj), None) == 0
+hdr = pkg.Array.from_buffer_copy(C.string_at(obj.value, 200))
+assert (hdr.num_rows, hdr.num_columns, hdr.effective_rank, hdr.flags) == (rows, n, k, pkg.FLAG_SVD)
+assert int(L.bsq_get_packed_size(obj)) == 200 + (rows * k + k + n * k) * 4
+assert L.bsq_decompress_initialize(rows, n, 0.0, 0.0, k, -1, -1, -1) == 0
+y = torch.zeros((rows, n), device="cuda")
+assert L.bsq_decompress(obj, y.data_ptr(), rows * n) == 0
+torch.cuda.synchronize()
+want = (u.double() * s.double()) @ v.double().T
+assert float((y.double() - want).norm() / want.norm()) <= 1e-6
+L.bsq_free(obj); L.bsq_decompress_release()
+L.bsq_shard_svd_destroy(h)
 np.savez(os.path.join(tmp, f"out{rank}.npz"), u=u.cpu().numpy(), s=s.cpu().numpy(), v=v.cpu().numpy())
 L.bsq_shard_comm_destroy(comm)
 '''
@@ -57,7 +80,12 @@ def test_row_sharded_svd_matches_unsharded(lib, tmp_path):
                    NCCL_NVLS_ENABLE="0")
         procs.append(subprocess.Popen([sys.executable, str(tmp_path / "worker.py")], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.PIPE, text=True))
-    outs = [p.communicate(timeout=300) for p in procs]
+    try:
+        outs = [p.communicate(timeout=300) for p in procs]
+    finally:
+        for p in procs:                      # a rank stuck in communicator set-up must not keep its GPU
+            if p.poll() is None:
+                p.kill()
     assert all(p.returncode == 0 for p in procs), outs
     r0, r1 = np.load(tmp_path / "out0.npz"), np.load(tmp_path / "out1.npz")
     # replicated factors are bit-identical on both ranks

@@ -50,7 +50,7 @@ def test_reconstruct_matches_fp64(lib, oracle, shape):
     d_out = torch.zeros((m, n), dtype=torch.float32, device="cuda")
     assert lib.bsq_reconstruct(dev(u).data_ptr(), dev(s).data_ptr(), dev(v).data_ptr(), m, n, k, None, d_out.data_ptr(), None, None, None) == 0
     torch.cuda.synchronize()
-    # FP32 accumulation over k terms against FP64: relative Frobenius error <= 1e-6 (SURVEY appendix C)
+    # FP32 accumulation over k terms against FP64: relative Frobenius error <= 1e-6
     assert rel_frob(want, d_out.cpu().numpy()) <= 1e-6
     # fused residual: minuend - product, flag set iff some |difference| > FLT_EPSILON
     r = want + np.float32(0.25)
@@ -188,7 +188,7 @@ def test_api_svd_roundtrip_and_layout(pkg, lib, oracle, oracle_mod, case):
     if ref is not None:
         assert ref.lib.ref_compress_initialize(rows, cols, outlier, err, rank, niters, uv, sfmt, -1, 1) == 0
         rb = ref.compress_bytes(d_a.data_ptr())
-        assert rb is not None and rb.size == packed.size or not (hdr.flags & pkg.FLAG_ERROR)
+        assert rb is not None and rb.size == packed.size
         assert ref.lib.ref_decompress_initialize(rows, cols, outlier, err, eff, uv, sfmt, -1) == 0
         h = ref.lib.ref_load_from_buffer(rb.ctypes.data, rb.size)
         r_y = torch.zeros_like(d_y)
