@@ -243,6 +243,8 @@ cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, c
         // (measured: the products are then bound by what the CTAs draw from L2, A once and B's images once per row
         // tile; that pays for tiles wider than 128 columns, where splitting B in every CTA is two thirds of the
         // staging work, and for long K)
+        // (up to 128 columns the register-staged kernel with two CTAs per SM measured faster than either image kernel:
+        // 67 against 80-88 us for 8192 x 128 x 4096)
         bool with_image = workspace && image_bytes + 128 <= workspace_bytes &&
                           (b_image_mode() == 2 ? M >= 256 : (b_image_mode() == 1 && M >= 512 && t.n_tile > 128 && K >= 1024));
         // a wide product (the reconstruction: N = a matrix dimension, K = the rank) in 256-column tiles, B's images
@@ -257,8 +259,23 @@ cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, c
         if (with_image) workspace_bytes = (workspace_bytes - image_room) & ~(size_t)127;
         const int tiles_tc = ((M + 127) / 128) * ((N + t.n_tile - 1) / t.n_tile);
         int splits_tc = 1;
-        const int slots = (with_image ? gemm_tc_image_ctas_per_sm(t.n_tile) : (t.n_tile <= 128 ? 2 : 1)) * sm_count;
-        if (with_image) gemm_tc_image_rings(t.n_tile, &t.a_stages, &t.b_stages);
+        if (with_image) {
+            // A contiguous along K comes in by TMA (one CTA per SM); the other orientation is staged through registers
+            t.b_image = reinterpret_cast<const float4 *>(workspace);      // placeholder for the check; set for good below
+            t.k_per_split = 32;
+            t.use_tma = gemm_tc_tma_usable(t, a_kmajor);
+            t.b_image = nullptr;
+            t.sm_count = sm_count;
+            if (t.use_tma && N > 256 && (minuend || kscale || tiles_tc >= sm_count)) {       // (no K split then)
+                // a wide product on the TMA-fed kernel: 128-column tiles (two accumulator sets fit tensor memory), walked
+                // by a persistent grid
+                t.n_tile = 128;
+                t.persistent = true;
+            }
+        }
+        const int slots = (t.use_tma ? 1 : with_image ? gemm_tc_image_ctas_per_sm(t.n_tile) : (t.n_tile <= 128 ? 2 : 1)) * sm_count;
+        if (t.use_tma) gemm_tc_tma_rings(t.n_tile, a_kmajor, &t.raw_stages, &t.a_stages, &t.b_stages);
+        else if (with_image) gemm_tc_image_rings(t.n_tile, &t.a_stages, &t.b_stages);
         if (workspace && !minuend && !kscale && tiles_tc < slots) {
             const int max_by_k = max(1, K / 256);             // a split below 256 of K costs more in the reduction than it gains
             const int max_by_ws = (int)(workspace_bytes / ((size_t)M * N * sizeof(float)));

@@ -21,7 +21,11 @@ struct GemmArgs {
     unsigned *flag;            // nullable: |= 1 when some |C| > FLT_EPSILON (with minuend)
     int n_tile;                // tensor-core kernel: columns per CTA (a multiple of 16, <= 256); grid.y tiles N
     const float4 *b_image;     // tensor-core kernel, nullable: room for B split beforehand (gemm_tc_image_bytes, 128-byte aligned)
-    int a_stages, b_stages;    // with b_image: ring lengths in shared memory (gemm_tc_image_rings)
+    int a_stages, b_stages;    // with b_image: ring lengths in shared memory (gemm_tc_image_rings / gemm_tc_tma_rings)
+    int raw_stages;            // TMA-fed kernel, A contiguous along M: slots of boxes as they come from memory
+    bool use_tma;              // with b_image: the kernel that brings A in by TMA (bsq_gemm_tma.cu)
+    bool persistent;           // with use_tma, no K split: one CTA per SM walks over all tiles (wide products)
+    int sm_count;
 };
 
 // Tensor-core path: true if the shape qualifies (N a multiple of 16, 16-byte aligned operands with leading
@@ -34,5 +38,13 @@ size_t gemm_tc_image_bytes(int N, int n_tile, int K);
 int gemm_tc_image_ctas_per_sm(int n_tile);
 void gemm_tc_image_rings(int n_tile, int *sa, int *nb);
 cudaError_t gemm_tc_launch(const GemmArgs &g, bool a_kmajor, bool b_kmajor, unsigned *status, cudaStream_t stream);
+
+// The TMA-fed kernel (bsq_gemm_tma.cu): A in either orientation, B split into images beforehand (g.b_image filled by
+// the caller of gemm_tc_tma_launch), one CTA per SM.  gemm_tc_tma_usable looks at the shape, the alignment and the
+// BSQ_GEMM_TMA switch; gemm_tc_tma_rings gives the ring lengths for raw_stages / a_stages / b_stages.
+bool gemm_tc_tma_enabled();
+bool gemm_tc_tma_usable(const GemmArgs &g, bool a_kmajor);
+void gemm_tc_tma_rings(int n_tile, bool a_kmajor, int *nraw, int *nr, int *nb);
+cudaError_t gemm_tc_tma_launch(const GemmArgs &g, bool a_kmajor, unsigned *status, cudaStream_t stream);
 
 }  // namespace bsq

@@ -1,0 +1,69 @@
+// Device helpers shared by the tensor-core product kernels (bsq_gemm_tc.cu, bsq_gemm_tma.cu): tcgen05 instruction and
+// descriptor wrappers, the TF32 split, and the layout of the operand images that a product's second operand is split
+// into beforehand.
+#pragma once
+
+#include "bsq_device.cuh"
+#include "bsq_gemm.hpp"
+
+namespace bsq {
+namespace {
+
+constexpr int TM = 128;          // output rows per CTA (UMMA M)
+constexpr int TK = 16;           // K per shared-memory stage (two k-steps of 8)
+constexpr int NT = 256;          // threads: all stage operands, one issues the MMAs, two per accumulator row in the epilogue
+constexpr int DEPTH = 3;         // chunks of K in flight in registers per thread
+constexpr int STAGES = 2;        // operand stages in shared memory (three measured slower: less L1 left for the loads)
+
+__device__ __forceinline__ uint64_t smem_desc(unsigned addr_bytes, unsigned lbo_bytes, unsigned sbo_bytes) {
+    // start address, leading / stride byte offsets in 16-byte units; version 1 (bits 46-47); no swizzle
+    return (uint64_t)((addr_bytes >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46);
+}
+
+__device__ __forceinline__ void mma_tf32(unsigned tmem_d, uint64_t desc_a, uint64_t desc_b, unsigned idesc, bool accumulate) {
+    const unsigned acc = accumulate ? 1u : 0u;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+
+// 16 consecutive accumulator columns of this thread's row (lane) of tensor memory
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+
+// Round to TF32 (10 mantissa bits), ties away from zero, by integer arithmetic on the bit pattern: two full-rate
+// instructions (add half of the last kept place, clear the 13 low bits; a carry out of the mantissa bumps the exponent
+// as it should).  Same result as cvt.rna.tf32.f32 for every finite value.
+__device__ __forceinline__ float tf32_rna(float x) {
+    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+}
+
+// x = hi + lo + e with hi, lo exactly representable in TF32 and |e| <= 2^-22 |x|
+__device__ __forceinline__ void split_store(float4 v, float4 *hi, float4 *lo) {
+    const float4 h = make_float4(tf32_rna(v.x), tf32_rna(v.y), tf32_rna(v.z), tf32_rna(v.w));
+    *hi = h;
+    *lo = make_float4(tf32_rna(__fsub_rn(v.x, h.x)), tf32_rna(__fsub_rn(v.y, h.y)), tf32_rna(__fsub_rn(v.z, h.z)),
+                      tf32_rna(__fsub_rn(v.w, h.w)));
+}
+
+// A B image is dense (nobody stores into it with a pattern that could conflict): core matrices of 8 columns x 16 B
+// follow one another along N every 128 B (SBO) and along K every extent * 16 B (LBO).
+__host__ __device__ constexpr unsigned image_half_units(int extent) { return (unsigned)(TK / 4) * (unsigned)extent; }
+__device__ __forceinline__ unsigned image_unit_index(int kc, int r, int extent) { return (unsigned)kc * (unsigned)extent + (unsigned)r; }
+// 16-byte units from one chunk's image to the next, and from one tile column's images to the next
+__host__ __device__ constexpr size_t image_units(int n_tile) { return 2 * (size_t)image_half_units(n_tile); }
+
+
+}  // namespace
+}  // namespace bsq

@@ -64,7 +64,9 @@ def test_nf4_threshold_table_in_kernel_header(oracle):
     block = block[:block.index("};")]
     thr = [int(v, 16) for v in re.findall(r"0x[0-9a-fA-F]{8}", block)]
     assert len(thr) == 32
-    real = sorted((np.array([t], np.uint32).view(np.float32)[0] for t in thr if t != 0x7F800000))
+    # buckets without a threshold hold NaN (never +Inf: "v >= +Inf" is true for v = +Inf and would give code 16)
+    assert 0x7F800000 not in thr
+    real = sorted((np.array([t], np.uint32).view(np.float32)[0] for t in thr if t != 0x7FC00000))
     assert len(real) == 15
     for i, t in enumerate(real):
         below = np.nextafter(np.float32(t), np.float32(-np.inf))
