@@ -6,8 +6,8 @@ Workload (the largest configuration of the path, BASELINE.json configs[4]): a ba
 matrices of 4096 x 14336 (per-layer seeds, seeded synthetic: low-rank + noise + outlier channels + heavy-tailed
 entries, bitsqueeze-llm_b200/workloads.py), full pipeline: outlier top-k 0.005, randomized SVD rank 256 with 2 power
 iterations, U/V in NF4, S in FP32, error-correction top-k 0.01; compress AND decompress.  Matrix i belongs to rank
-i % N (one process per GPU, no collective on the data path: the matrices are independent, weak-free strong split of a
-fixed batch).  A step is one pass over the rank's share of the batch: every matrix compressed, then every object
+i % N (one process per GPU, no collective on the data path: the matrices are independent; the batch is fixed, so more
+GPUs means fewer matrices per GPU: strong scaling).  A step is one pass over the rank's share of the batch: every matrix compressed, then every object
 decompressed.  Inputs (235 MB each) are larger than the L2.
 
   value   FP32 bytes of the whole batch / time of a step, inputs resident in HBM, packed objects left in device
@@ -16,8 +16,8 @@ decompressed.  Inputs (235 MB each) are larger than the L2.
           beside it, and the same with one matrix at a time (lanes = 1).
   e2e     the same step with HOST buffers: matrices in pinned host memory, packed objects returned as host objects
           (the public object format), decompress from those host objects; host<->device copies inside the timed region.
-  roofline      the tcgen05 3xTF32 product kernel (gemm_tc_image_kernel: the six products of the range finder with the
-                4096 x 14336 matrix), timed by CUDA events on its stream in a one-lane pass; FLOPs 2 M N K per launch
+  roofline      the TMA-fed tcgen05 3xTF32 product kernel (gemm_tc_tma_kernel: the six products of the range finder with
+                the 4096 x 14336 matrix), timed by CUDA events on its stream in a one-lane pass; FLOPs 2 M N K per launch
                 against the TF32 dense rate measured in this run / 3.
   cpu_baseline  rank 0, N=1: the only stage of this pipeline the reference can run on a CPU -- its OpenMP NF4 quantiser
                 (oracle/_ref/libref_cpu.so) on arrays of U's and V's size -- on all host cores.
@@ -49,8 +49,8 @@ WORKLOAD = ("configs[4]: 32 independent 4096x14336 FP32 matrices, outlier_topk=0
             "U/V NF4, S FP32, error_correction_topk=0.01, compress+decompress, matrix i on rank i % N")
 # kernels this library launches per matrix in this configuration (ncu launch list of `--single C5A`; the figure is
 # stated next to the list in profiles/)
-LAUNCHES_PER_COMPRESS = 96
-LAUNCHES_PER_DECOMPRESS = 7
+LAUNCHES_PER_COMPRESS = 57
+LAUNCHES_PER_DECOMPRESS = 6
 
 
 def workloads():
@@ -728,7 +728,7 @@ def main():
                            "matrix), the lanes form of bitsqz_llm_compress / bitsqz_llm_decompress; h2d = inputs + objects on their way "
                            "back for decompress"},
             "gpu_launches": (LAUNCHES_PER_COMPRESS + LAUNCHES_PER_DECOMPRESS) * n_layers * passes * nsteps,
-            "roofline": {"bound": "tensor", "kernel": "gemm_tc_image_kernel<*,256> (tcgen05 3xTF32, 4096x14336 matrix times a 256-column panel)",
+            "roofline": {"bound": "tensor", "kernel": "gemm_tc_tma_kernel<*,256> (TMA-fed tcgen05 3xTF32, 4096x14336 matrix times a 256-column panel)",
                          "achieved": ach, "peak": peak3, "unit": "TFLOP/s", "frac": (ach / peak3) if ach else None, "traffic": None,
                          "peak_kind": "TF32 dense matmul measured in this run (%.0f TFLOP/s) / 3; BF16 %s %.0f" % (tf32, peak_kind, bf16_peak),
                          "flops_per_launch": flops, "ms_per_launch": prod_mean, "launches_timed": len(prod_ms),
