@@ -208,10 +208,12 @@ struct FrontGeometry {
 FrontGeometry front_geometry(uint32_t cols, int code_buffers) {
     FrontGeometry f;
     f.G = cols <= 2048 ? 2 : (cols <= 8192 ? 4 : 8);        // measured on 4096-column rows: 4 warps per row is best
-    if (const char *e = getenv("BSQ_FRONT_G")) {             // tuning override: warps per row
-        const int v = atoi(e);
-        if (v == 1 || v == 2 || v == 4 || v == 8) f.G = v;
-    }
+    static const int forced_g = [] {                         // tuning override, read once: warps per row
+        const char *e = getenv("BSQ_FRONT_G");
+        const int v = e ? atoi(e) : 0;
+        return (v == 1 || v == 2 || v == 4 || v == 8) ? v : 0;
+    }();
+    if (forced_g) f.G = forced_g;
     f.threads = 256;
     f.groups = f.threads / (32 * f.G);
     f.smem = stream_layout(cols, code_buffers).total * f.groups;

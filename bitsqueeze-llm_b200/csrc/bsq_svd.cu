@@ -1018,7 +1018,10 @@ SvdWorkspace *svd_workspace_create_sharded(int m, int n, int k, int niter, int s
         // Jacobi stops when the columns are orthogonal to this tolerance; the library's default is machine epsilon.
         // The factors only have to carry FP32 products to ~1e-6, and every sweep over a 256 x 256 core costs 0.4 ms.
         double tol = 1.0e-6;
-        if (const char *e = getenv("BSQ_CORE_SVD_TOL")) tol = atof(e);
+        if (const char *e = getenv("BSQ_CORE_SVD_TOL")) {
+            const double v = atof(e);
+            if (v >= 1.0e-8 && v <= 1.0e-2) tol = v;          // anything else: keep the default
+        }
         ok = ok && cusolverDnXgesvdjSetTolerance(ws->svdj, tol) == CUSOLVER_STATUS_SUCCESS;
     }
     if (ok) {
