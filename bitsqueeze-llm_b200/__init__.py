@@ -92,6 +92,7 @@ SIGNATURES = {
     "bsq_shard_svd_destroy": (None, [_vp]),
     "bsq_shard_svd_run": (_i, [_vp, _vp, C.c_ulonglong, _vp, _vp, _vp, _vp]),
     "bsq_shard_compress": (_i, [_vp, _vp, C.c_ulonglong, C.POINTER(_vp), _vp]),
+    "bsq_shard_uses_peer_exchange": (_i, [_vp]),
     "bsq_shard_svd_profile": (_i, [_vp, _i]),
     "bsq_shard_svd_profile_read": (_i, [_vp, _vp, _vp, _i]),
     "bsq_lane_create": (_vp, [_u16, _u16, _f, _f, _i, _i, _i, _i, _i]),

@@ -276,7 +276,11 @@ __device__ __forceinline__ float group_topk_row(const RowGroup<G> &g, GroupCtl &
         }
     }
     group_rank_emit<G>(g, c, row, count, k, out_idx, out_val, zero_selected);
-    return __uint_as_float(c.kth_bits) * 0.9375f;
+    // The next row's guess: a little below this row's k-th largest, so that between k and kCandCap of its elements
+    // reach it.  The window is narrow for a large k (143 of 256: a Gaussian tail has 225 elements above 0.9375 of the
+    // k-th largest, too close to the cap and beyond the 256 float4 the first sweep can note), so the margin shrinks
+    // with k; a guess that misses only costs the row a second and third sweep, never the result.
+    return __uint_as_float(c.kth_bits) * (k <= 96u ? 0.9375f : 0.9609375f);
 }
 
 // Block maxima of the (zeroed) row: blk_out[b] = absmax of block b, 1.0 for a block of zeros

@@ -428,7 +428,7 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const fl
             if (i < k && c < k) {
                 const size_t e = (size_t)i * k + c;
                 if (c < i) {
-                    T[e] = 0.0f;
+                    if (T) T[e] = 0.0f;
                     if (Rcpy) Rcpy[e] = 0.0f;
                 } else if (Rcpy) {
                     Rcpy[e] = blocks[(size_t)blk_id(I, Jb, nb) * kCB * kCB + tid];
@@ -436,6 +436,7 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const fl
             }
         }
     }
+    if (!T) return;                                         // only the factor was wanted (uniform over the CTA)
     if (warp < nb) {
         const float *D = blocks + (size_t)blk_id(warp, warp, nb) * kCB * kCB;
         float a[kCB], t[kCB];
@@ -665,7 +666,10 @@ __device__ __forceinline__ void st_async_f4(unsigned dst, const float4 &v, unsig
                  : "memory");
 }
 
-template <int kJcLen, int kLpp>
+// kWithV = false leaves the right factor out: nothing accumulates the rotations (half the shared-memory traffic of a
+// round), and Vcol receives column j of M divided by S(j)^2 instead -- the k x k matrix that turns the panel the core
+// came from into its singular vectors (B^T v_j / S(j) with v_j = M(:, j) / S(j)).
+template <int kJcLen, int kLpp, bool kWithV>
 __global__ void __launch_bounds__(kJcLen / 2 * kLpp, 1) jacobi_svd_cluster_kernel(const float *__restrict__ C, int k, float *__restrict__ S,
                                                                         float *__restrict__ Ucol, float *__restrict__ Vcol,
                                                                         unsigned *__restrict__ status) {
@@ -717,7 +721,7 @@ __global__ void __launch_bounds__(kJcLen / 2 * kLpp, 1) jacobi_svd_cluster_kerne
             const int e = e0 + u * nt, j = e / kJcRows, i = row0 + e % kJcRows;
             if (e < kp * kJcRows) {
                 M[e] = v[u];
-                V[e] = (i == j && j < k) ? 1.0f : 0.0f;
+                if (kWithV) V[e] = (i == j && j < k) ? 1.0f : 0.0f;
             }
         }
     }
@@ -771,7 +775,7 @@ __global__ void __launch_bounds__(kJcLen / 2 * kLpp, 1) jacobi_svd_cluster_kerne
     float dv_c = 1.0f, dv_sn = 0.0f;
     bool dv_pending = false;
     auto apply_to_v = [&]() {
-        if (!dv_pending) return;
+        if (!kWithV || !dv_pending) return;
         float4 *vp = reinterpret_cast<float4 *>(V + (size_t)dv_p * kJcRows), *vq = reinterpret_cast<float4 *>(V + (size_t)dv_q * kJcRows);
         const float c = dv_c, sn = dv_sn;
 #pragma unroll
@@ -877,7 +881,7 @@ __global__ void __launch_bounds__(kJcLen / 2 * kLpp, 1) jacobi_svd_cluster_kerne
             const float sj = nrm[j];
             const size_t o = (size_t)rank_of[j] * k + i;
             Ucol[o] = sj > 0.0f ? M[e] / sj : 0.0f;
-            Vcol[o] = V[e];
+            Vcol[o] = kWithV ? V[e] : (sj > 0.0f ? M[e] / (sj * sj) : 0.0f);
         }
     }
     cluster.sync();                                           // nobody leaves while a neighbour could still store into it
@@ -928,11 +932,14 @@ bool alloc_f(float **p, size_t count) {
 // one is enough to keep a power iteration stable, two give orthonormality to rounding.  `tmp` is a
 // second rows x k buffer; the result ends in Y for 2 passes and in tmp for 1 (returned through *out).
 // r_a / r_b (nullable) receive the triangular factors of the passes (Y_in = Y_out * r_b * r_a).
+// last_factor_only: the last pass stops after its Cholesky factor (no inverse, no panel product): the caller wants the
+// triangular factors only, and Y itself is left as it was (k <= kCholeskyBlockedMaxK).
 cudaError_t orthonormalise(SvdWorkspace *ws, float *Y, float *tmp, int rows, int passes, float *r_a, float *r_b,
-                           float **out, bool sharded_rows, cudaStream_t st) {
+                           float **out, bool sharded_rows, cudaStream_t st, bool last_factor_only = false) {
     const int k = ws->k;
     float *src = Y, *dst = tmp;
     for (int pass = 0; pass < passes; ++pass) {
+        const bool factor_only = last_factor_only && pass + 1 == passes;
         // G = src^T src
         cudaError_t err = gemm(false, false, src, k, src, k, ws->g, k, k, k, rows, nullptr, nullptr, 0, nullptr, ws->status, ws->gemm_ws,
                                ws->gemm_ws_bytes, ws->sm_count, st);
@@ -941,7 +948,7 @@ cudaError_t orthonormalise(SvdWorkspace *ws, float *Y, float *tmp, int rows, int
         // every rank then factors the same k x k matrix and gets bit-identical R
         if (sharded_rows && ws->allreduce && (err = timed_allreduce(ws, ws->g, (size_t)k * k, st)) != cudaSuccess) return err;
         if (k <= kCholeskyBlockedMaxK) {
-            cholesky_inverse_blocked_kernel<<<1, 1024, cholesky_blocked_smem_bytes(k), st>>>(ws->g, k, ws->t,
+            cholesky_inverse_blocked_kernel<<<1, 1024, cholesky_blocked_smem_bytes(k), st>>>(ws->g, k, factor_only ? nullptr : ws->t,
                                                                                                 pass == 0 ? r_a : r_b);
         } else if (k <= kCholeskySmemMaxK) {
             cholesky_inverse_smem_kernel<<<1, 1024, cholesky_smem_bytes(k), st>>>(ws->g, k, ws->t, pass == 0 ? r_a : r_b);
@@ -950,6 +957,7 @@ cudaError_t orthonormalise(SvdWorkspace *ws, float *Y, float *tmp, int rows, int
         }
         err = cudaGetLastError();
         if (err != cudaSuccess) return err;
+        if (factor_only) break;
         // dst = src T
         err = gemm(true, false, src, k, ws->t, k, dst, k, rows, k, k, nullptr, nullptr, 0, nullptr, ws->status, ws->gemm_ws,
                    ws->gemm_ws_bytes, ws->sm_count, st);
@@ -1043,11 +1051,11 @@ SvdWorkspace *svd_workspace_create_sharded(int m, int n, int k, int niter, int s
     if (ok && ws->own_core_svd && ws->k > kJacobiSingleMaxK) {
         const char *e = getenv("BSQ_JACOBI_LPP");
         ws->jc_lanes = ws->k <= 128 || (e && atoi(e) == 4) ? 4 : 2;
-        ok = (ws->k <= 128        ? cudaFuncSetAttribute(jacobi_svd_cluster_kernel<128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        ok = (ws->k <= 128        ? cudaFuncSetAttribute(jacobi_svd_cluster_kernel<128, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                          (int)jacobi_cluster_smem_bytes(ws->k))
-              : ws->jc_lanes == 4 ? cudaFuncSetAttribute(jacobi_svd_cluster_kernel<256, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+              : ws->jc_lanes == 4 ? cudaFuncSetAttribute(jacobi_svd_cluster_kernel<256, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                          (int)jacobi_cluster_smem_bytes(ws->k))
-                                  : cudaFuncSetAttribute(jacobi_svd_cluster_kernel<256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  : cudaFuncSetAttribute(jacobi_svd_cluster_kernel<256, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                          (int)jacobi_cluster_smem_bytes(ws->k))) == cudaSuccess;
         if (ok) {
             // a device (or partition of one) that cannot place a cluster of 8 such CTAs keeps the library solver
@@ -1055,9 +1063,9 @@ SvdWorkspace *svd_workspace_create_sharded(int m, int n, int k, int niter, int s
             cudaLaunchAttribute attr[1];
             jacobi_cluster_config(&cfg, attr, ws->k, ws->jc_lanes, nullptr);
             int clusters = 0;
-            const cudaError_t q = ws->k <= 128        ? cudaOccupancyMaxActiveClusters(&clusters, jacobi_svd_cluster_kernel<128, 4>, &cfg)
-                                  : ws->jc_lanes == 4 ? cudaOccupancyMaxActiveClusters(&clusters, jacobi_svd_cluster_kernel<256, 4>, &cfg)
-                                                      : cudaOccupancyMaxActiveClusters(&clusters, jacobi_svd_cluster_kernel<256, 2>, &cfg);
+            const cudaError_t q = ws->k <= 128        ? cudaOccupancyMaxActiveClusters(&clusters, jacobi_svd_cluster_kernel<128, 4, false>, &cfg)
+                                  : ws->jc_lanes == 4 ? cudaOccupancyMaxActiveClusters(&clusters, jacobi_svd_cluster_kernel<256, 4, false>, &cfg)
+                                                      : cudaOccupancyMaxActiveClusters(&clusters, jacobi_svd_cluster_kernel<256, 2, false>, &cfg);
             if (q != cudaSuccess || clusters < 1) {
                 cudaGetLastError();
                 ws->own_core_svd = false;
@@ -1167,9 +1175,12 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
             cudaSuccess)
             return err;
     }
-    // B^T = W^T Q = Q2 C with C = R2 R1
+    // B^T = W^T Q = Q2 C with C = R2 R1.  With the cluster Jacobi kernel the right factor comes from the panel B^T
+    // itself (B^T v_j / S(j)), so Q2 is never formed: the second pass only has to deliver R2.
+    const bool from_panel = ws->own_core_svd && k > kJacobiSingleMaxK;
     if ((err = times_w(ws, d_A, true, q, false, ws->z, st)) != cudaSuccess) return err;
-    if ((err = orthonormalise(ws, ws->z, ws->z2, ws->N, 2, ws->tinv1, ws->tinv2, &qz, false, st)) != cudaSuccess) return err;
+    if ((err = orthonormalise(ws, ws->z, ws->z2, ws->N, 2, ws->tinv1, ws->tinv2, &qz, false, st, from_panel)) != cudaSuccess) return err;
+    if (from_panel) qz = ws->z;
     if ((err = gemm(true, false, ws->tinv2, k, ws->tinv1, k, ws->core, k, k, k, k, nullptr, nullptr, 0, nullptr, ws->status, nullptr, 0,
                     ws->sm_count, st)) != cudaSuccess)
         return err;
@@ -1181,9 +1192,9 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
         const float *core = ws->core;
         float *vc = ws->vc, *uc = ws->uc;
         unsigned *status = ws->status;
-        err = k <= 128            ? cudaLaunchKernelEx(&cfg, jacobi_svd_cluster_kernel<128, 4>, core, k, d_S, vc, uc, status)
-              : ws->jc_lanes == 4 ? cudaLaunchKernelEx(&cfg, jacobi_svd_cluster_kernel<256, 4>, core, k, d_S, vc, uc, status)
-                                  : cudaLaunchKernelEx(&cfg, jacobi_svd_cluster_kernel<256, 2>, core, k, d_S, vc, uc, status);
+        err = k <= 128            ? cudaLaunchKernelEx(&cfg, jacobi_svd_cluster_kernel<128, 4, false>, core, k, d_S, vc, uc, status)
+              : ws->jc_lanes == 4 ? cudaLaunchKernelEx(&cfg, jacobi_svd_cluster_kernel<256, 4, false>, core, k, d_S, vc, uc, status)
+                                  : cudaLaunchKernelEx(&cfg, jacobi_svd_cluster_kernel<256, 2, false>, core, k, d_S, vc, uc, status);
         if (err != cudaSuccess) return err;
     } else if (ws->own_core_svd) {
         jacobi_svd_kernel<<<1, 512, jacobi_smem_bytes(k), st>>>(ws->core, k, d_S, ws->vc, ws->uc);
@@ -1192,7 +1203,8 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
                                  ws->solver_work, ws->lwork, ws->dev_info, ws->svdj) != CUSOLVER_STATUS_SUCCESS) {
         return cudaErrorUnknown;
     }
-    // W = (Q Vc) S (Q2 Uc)^T; both k x k factors are column-major, i.e. K-major B operands
+    // W = (Q Vc) S (Q2 Uc)^T; both k x k factors are column-major, i.e. K-major B operands.  (from_panel: qz is the
+    // panel B^T itself and column j of uc is Vc(:, j) / S(j): B^T Vc(:, j) / S(j) is the vector Q2 Uc(:, j).)
     float *d_left = ws->transposed ? d_V : d_U;            // M x k factor
     float *d_right = ws->transposed ? d_U : d_V;           // N x k factor
     if ((err = gemm(true, true, q, k, ws->vc, k, d_left, k, ws->M, k, k, nullptr, nullptr, 0, nullptr, ws->status, ws->gemm_ws, ws->gemm_ws_bytes,

@@ -174,6 +174,9 @@ int bsq_shard_svd_run(bsq_shard_svd_t *handle, const float *d_A_local, unsigned 
                       float *d_V, void *stream);
 int bsq_shard_compress(bsq_shard_svd_t *handle, const float *d_A_local, unsigned long long seed, struct bitsqz_llm_array **out,
                        void *stream);
+/* 1 if this communicator's k x k all-reduces run as one kernel over peer memory (ranks that can map each other's memory
+ * through CUDA IPC: the GPUs of one node), 0 if they go through NCCL like the large ones (BSQ_SHARD_PEER=0 forces that) */
+int bsq_shard_uses_peer_exchange(void *comm);
 int bsq_shard_svd_profile(bsq_shard_svd_t *handle, int on);
 int bsq_shard_svd_profile_read(bsq_shard_svd_t *handle, float *ms, int *kinds, int capacity);
 

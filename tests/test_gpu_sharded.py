@@ -61,12 +61,16 @@ want = (u.double() * s.double()) @ v.double().T
 assert float((y.double() - want).norm() / want.norm()) <= 1e-6
 L.bsq_free(obj); L.bsq_decompress_release()
 L.bsq_shard_svd_destroy(h)
-np.savez(os.path.join(tmp, f"out{rank}.npz"), u=u.cpu().numpy(), s=s.cpu().numpy(), v=v.cpu().numpy())
+np.savez(os.path.join(tmp, f"out{rank}.npz"), u=u.cpu().numpy(), s=s.cpu().numpy(), v=v.cpu().numpy(),
+         peer=np.int32(L.bsq_shard_uses_peer_exchange(comm)))
 L.bsq_shard_comm_destroy(comm)
 '''
 
 
-def test_row_sharded_svd_matches_unsharded(lib, tmp_path):
+@pytest.mark.parametrize("peer", ["1", "0"], ids=["peer-exchange", "nccl-only"])
+def test_row_sharded_svd_matches_unsharded(lib, tmp_path, peer):
+    """peer-exchange: the k x k all-reduces run as one kernel over peer memory where the ranks can map each other's
+    memory (falls back to NCCL otherwise, which the saved flag tells); nccl-only: BSQ_SHARD_PEER=0."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     from test_gpu_svd import lowrank_plus_noise, rel_frob, svd_gpu
@@ -77,7 +81,7 @@ def test_row_sharded_svd_matches_unsharded(lib, tmp_path):
     procs = []
     for rank in range(2):
         env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", BSQ_ROOT=ROOT, BSQ_TMP=str(tmp_path), BSQ_K=str(k),
-                   NCCL_NVLS_ENABLE="0")
+                   NCCL_NVLS_ENABLE="0", BSQ_SHARD_PEER=peer)
         procs.append(subprocess.Popen([sys.executable, str(tmp_path / "worker.py")], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.PIPE, text=True))
     try:
@@ -88,6 +92,9 @@ def test_row_sharded_svd_matches_unsharded(lib, tmp_path):
                 p.kill()
     assert all(p.returncode == 0 for p in procs), outs
     r0, r1 = np.load(tmp_path / "out0.npz"), np.load(tmp_path / "out1.npz")
+    assert int(r0["peer"]) == int(r1["peer"])                  # both ranks agree on how they exchange
+    if peer == "0":
+        assert int(r0["peer"]) == 0
     # replicated factors are bit-identical on both ranks
     assert np.array_equal(r0["s"].view(np.uint32), r1["s"].view(np.uint32))
     assert np.array_equal(r0["v"].view(np.uint32), r1["v"].view(np.uint32))
