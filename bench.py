@@ -128,6 +128,33 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def bind_near_gpu(gpu_index):
+    """Best effort: run this process (and so first-touch its pinned host buffers) on the NUMA node the GPU hangs off.
+    Changes only this process's CPU affinity.  Returns a short description for the bench line."""
+    try:
+        bus = subprocess.run(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=pci.bus_id", "--format=csv,noheader"],
+                             capture_output=True, text=True, timeout=20).stdout.strip().lower()
+        if not bus:
+            return "unknown (no bus id)"
+        dom, rest = bus.split(":", 1)
+        path = "/sys/bus/pci/devices/%s:%s/numa_node" % (dom[-4:], rest)
+        node = int(open(path).read().strip())
+        if node < 0:
+            return "no NUMA information for %s" % bus
+        cpus = set()
+        for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0)
+        use = cpus & allowed
+        if not use:
+            return "GPU on node %d, but this process may only run on other nodes' CPUs: left as it is" % node
+        os.sched_setaffinity(0, use)
+        return "bound to the %d CPUs of NUMA node %d next to the GPU" % (len(use), node)
+    except Exception as e:                                   # noqa: BLE001 -- any failure just leaves the affinity alone
+        return "not bound (%s)" % type(e).__name__
+
+
 def rel_frob(x, y):
     return float((x.double() - y.double()).norm() / x.double().norm())
 
@@ -548,6 +575,8 @@ def main():
     import torch
     import torch.distributed as dist
 
+    all_cpus = os.sched_getaffinity(0) if hasattr(os, "sched_getaffinity") else None
+    numa = bind_near_gpu(local_rank)
     pkg = entry.load_package()
     L = pkg.lib()
     W = workloads()
@@ -749,7 +778,7 @@ def main():
             "config": {"workload": WORKLOAD, "rows": rows, "cols": cols, "layers": n_layers, "passes_per_step": passes,
                        "lanes_per_gpu": lanes,
                        "parallelism": "matrix i on rank i %% %d, no collective on the data path; %d matrices in flight per GPU" % (world, lanes),
-                       "l2": "every input matrix is 235 MB (> 126 MB L2)",
+                       "l2": "every input matrix is 235 MB (> 126 MB L2)", "host_memory": "rank 0: " + numa,
                        "timed_region_s": ms_total * 1e-3},
             "compress": {"value": per_step * nsteps / (ms_c * 1e-3) / 1e9, "unit": "GB/s", "ms_per_matrix": ms_c / (nsteps * passes * max(cnt, 1)),
                          "one_at_a_time_ms_per_matrix": one_c},
@@ -782,6 +811,8 @@ def main():
         if not args.skip_extras:
             line["configs1_frontend"] = c2_frontend_leg(torch, pkg, L, W, hbm_peak)
             if world == 1:
+                if all_cpus:
+                    os.sched_setaffinity(0, all_cpus)         # the CPU baseline runs on every core this process may use
                 line["cpu_baseline"] = cpu_nf4_baseline(W)
         print(json.dumps(line))
     if world > 1:
