@@ -560,6 +560,9 @@ def main():
                     help="side measurement, not the bench line: public compress / decompress of one matrix")
     ap.add_argument("--skip-extras", action="store_true", help="leave out the configs[1] leg, the row-sharded leg and the CPU baseline")
     ap.add_argument("--sharded-only", action="store_true", help="run only the row-sharded SVD leg (needs torchrun, N >= 2)")
+    ap.add_argument("--stage-only", action="store_true",
+                    help="run only the configs[1] leg (fused front end and fused decompress kernel, device resident): for "
+                         "profiler captures; prints that leg's figures, no bench line")
     args = ap.parse_args()
     if args.single:
         run_single(args)
@@ -590,6 +593,10 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.stage_only:
+        if rank == 0:
+            print(json.dumps({"stage_only": True, "configs1_frontend": c2_frontend_leg(torch, pkg, L, W, measured_peaks()[0])}))
+        return
     if args.sharded_only:
         res = row_sharded_leg(torch, dist, pkg, L, W, rank, world)
         if rank == 0:

@@ -60,6 +60,7 @@ struct SvdWorkspace {
     unsigned *status = nullptr;         // device status word of the current call
     unsigned *own_status = nullptr;     // used when the caller passes none
     int jc_lanes = 4;                   // lanes per column pair of the cluster Jacobi kernel for this k
+    bool jc_with_v = false;             // ... and whether it accumulates the right factor (else that comes from the panel)
     bool own_core_svd = false;          // k small enough for jacobi_svd_kernel (else cuSOLVER's gesvdj on the core)
     bool seeded = false;                // omega holds the draw for `seed`
     unsigned long long seed = 0, offset = 0;
@@ -834,7 +835,14 @@ __global__ void __launch_bounds__(kJcLen / 2 * kLpp, 1) jacobi_svd_cluster_kerne
                     st_async_f4(part_to + par * (unsigned)(kJcCtas * kSlots * sizeof(float)), g4, mbar_to + par * (unsigned)sizeof(uint64_t));
             }
             apply_to_v();                                     // the previous round's rotation of V, while the stores travel
-            if (!failed) failed = !mbar_wait_bounded(&mbar[par], phase, status);
+            // one lane per warp polls the barrier (256 polling threads get in the way of the stores that are arriving in
+            // this CTA's shared memory); the warp's other lanes take its word
+            {
+                int got = 1;
+                if (lane == 0 && !failed) got = mbar_wait_bounded(&mbar[par], phase, status) ? 1 : 0;
+                got = __shfl_sync(0xffffffffu, got, 0);
+                if (!got) failed = true;
+            }
             const float *pp = part + par * kJcCtas * kSlots + slot;
             g = ((pp[0] + pp[kSlots]) + (pp[2 * kSlots] + pp[3 * kSlots])) + ((pp[4 * kSlots] + pp[5 * kSlots]) + (pp[6 * kSlots] + pp[7 * kSlots]));
             if (active && alpha > 0.0f && beta > 0.0f && g * g > tol2 * alpha * beta) {
@@ -885,6 +893,15 @@ __global__ void __launch_bounds__(kJcLen / 2 * kLpp, 1) jacobi_svd_cluster_kerne
         }
     }
     cluster.sync();                                           // nobody leaves while a neighbour could still store into it
+}
+
+// The instance of the cluster kernel for a core of k columns: `lanes` threads per pair slot, with or without the
+// accumulated right factor.
+typedef void (*JacobiClusterFn)(const float *, int, float *, float *, float *, unsigned *);
+JacobiClusterFn jacobi_cluster_fn(int k, int lanes, bool with_v) {
+    if (k <= 128) return with_v ? jacobi_svd_cluster_kernel<128, 4, true> : jacobi_svd_cluster_kernel<128, 4, false>;
+    if (lanes == 4) return with_v ? jacobi_svd_cluster_kernel<256, 4, true> : jacobi_svd_cluster_kernel<256, 4, false>;
+    return with_v ? jacobi_svd_cluster_kernel<256, 2, true> : jacobi_svd_cluster_kernel<256, 2, false>;
 }
 
 // Launch configuration of the cluster kernel: one cluster of kJcCtas CTAs, `lanes` threads per pair slot.
@@ -1051,21 +1068,19 @@ SvdWorkspace *svd_workspace_create_sharded(int m, int n, int k, int niter, int s
     if (ok && ws->own_core_svd && ws->k > kJacobiSingleMaxK) {
         const char *e = getenv("BSQ_JACOBI_LPP");
         ws->jc_lanes = ws->k <= 128 || (e && atoi(e) == 4) ? 4 : 2;
-        ok = (ws->k <= 128        ? cudaFuncSetAttribute(jacobi_svd_cluster_kernel<128, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                         (int)jacobi_cluster_smem_bytes(ws->k))
-              : ws->jc_lanes == 4 ? cudaFuncSetAttribute(jacobi_svd_cluster_kernel<256, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                         (int)jacobi_cluster_smem_bytes(ws->k))
-                                  : cudaFuncSetAttribute(jacobi_svd_cluster_kernel<256, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                         (int)jacobi_cluster_smem_bytes(ws->k))) == cudaSuccess;
+        {
+            const char *v = getenv("BSQ_JACOBI_V");           // 1 / 0: with / without the accumulated right factor (A/B comparisons)
+            ws->jc_with_v = v ? v[0] == '1' : false;
+        }
+        ok = cudaFuncSetAttribute(jacobi_cluster_fn(ws->k, ws->jc_lanes, ws->jc_with_v), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)jacobi_cluster_smem_bytes(ws->k)) == cudaSuccess;
         if (ok) {
             // a device (or partition of one) that cannot place a cluster of 8 such CTAs keeps the library solver
             cudaLaunchConfig_t cfg = {};
             cudaLaunchAttribute attr[1];
             jacobi_cluster_config(&cfg, attr, ws->k, ws->jc_lanes, nullptr);
             int clusters = 0;
-            const cudaError_t q = ws->k <= 128        ? cudaOccupancyMaxActiveClusters(&clusters, jacobi_svd_cluster_kernel<128, 4, false>, &cfg)
-                                  : ws->jc_lanes == 4 ? cudaOccupancyMaxActiveClusters(&clusters, jacobi_svd_cluster_kernel<256, 4, false>, &cfg)
-                                                      : cudaOccupancyMaxActiveClusters(&clusters, jacobi_svd_cluster_kernel<256, 2, false>, &cfg);
+            const cudaError_t q = cudaOccupancyMaxActiveClusters(&clusters, jacobi_cluster_fn(ws->k, ws->jc_lanes, ws->jc_with_v), &cfg);
             if (q != cudaSuccess || clusters < 1) {
                 cudaGetLastError();
                 ws->own_core_svd = false;
@@ -1177,7 +1192,7 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
     }
     // B^T = W^T Q = Q2 C with C = R2 R1.  With the cluster Jacobi kernel the right factor comes from the panel B^T
     // itself (B^T v_j / S(j)), so Q2 is never formed: the second pass only has to deliver R2.
-    const bool from_panel = ws->own_core_svd && k > kJacobiSingleMaxK;
+    const bool from_panel = ws->own_core_svd && k > kJacobiSingleMaxK && !ws->jc_with_v;
     if ((err = times_w(ws, d_A, true, q, false, ws->z, st)) != cudaSuccess) return err;
     if ((err = orthonormalise(ws, ws->z, ws->z2, ws->N, 2, ws->tinv1, ws->tinv2, &qz, false, st, from_panel)) != cudaSuccess) return err;
     if (from_panel) qz = ws->z;
@@ -1192,9 +1207,7 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
         const float *core = ws->core;
         float *vc = ws->vc, *uc = ws->uc;
         unsigned *status = ws->status;
-        err = k <= 128            ? cudaLaunchKernelEx(&cfg, jacobi_svd_cluster_kernel<128, 4, false>, core, k, d_S, vc, uc, status)
-              : ws->jc_lanes == 4 ? cudaLaunchKernelEx(&cfg, jacobi_svd_cluster_kernel<256, 4, false>, core, k, d_S, vc, uc, status)
-                                  : cudaLaunchKernelEx(&cfg, jacobi_svd_cluster_kernel<256, 2, false>, core, k, d_S, vc, uc, status);
+        err = cudaLaunchKernelEx(&cfg, jacobi_cluster_fn(k, ws->jc_lanes, ws->jc_with_v), core, k, d_S, vc, uc, status);
         if (err != cudaSuccess) return err;
     } else if (ws->own_core_svd) {
         jacobi_svd_kernel<<<1, 512, jacobi_smem_bytes(k), st>>>(ws->core, k, d_S, ws->vc, ws->uc);
