@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--lanes L]
 
-Workload (the largest configuration of the path, BASELINE.json configs[4]): a batch of 32 independent FP32 activation
+Workload (the largest configuration of the path, benchmark configuration 5, configs[4]): a batch of 32 independent FP32 activation
 matrices of 4096 x 14336 (per-layer seeds, seeded synthetic: low-rank + noise + outlier channels + heavy-tailed
 entries, bitsqueeze-llm_b200/workloads.py), full pipeline: outlier top-k 0.005, randomized SVD rank 256 with 2 power
 iterations, U/V in NF4, S in FP32, error-correction top-k 0.01; compress AND decompress.  Matrix i belongs to rank
@@ -47,9 +47,9 @@ import __graft_entry__ as entry  # noqa: E402
 METRIC = "FP32-input GB/s, compress+decompress of 32 x (4096x14336) FP32 matrices, full pipeline"
 WORKLOAD = ("configs[4]: 32 independent 4096x14336 FP32 matrices, outlier_topk=0.005, SVD rank 256 (2 power iterations), "
             "U/V NF4, S FP32, error_correction_topk=0.01, compress+decompress, matrix i on rank i % N")
-# kernels this library launches per matrix in this configuration (ncu launch list of `--single C5A`; the figure is
-# stated next to the list in profiles/)
-LAUNCHES_PER_COMPRESS = 57
+# kernels this library launches per matrix in this configuration, counted from an ncu launch list of
+# `python bench.py --single C5A` (all launches of the run, minus the decompress calls', divided by the compress calls)
+LAUNCHES_PER_COMPRESS = 56
 LAUNCHES_PER_DECOMPRESS = 6
 
 

@@ -77,7 +77,7 @@ def glibc_uniform(seed, n, lo=-10.0, hi=10.0):
 
 
 def make_c2_like(rows, cols, seed, outlier_frac=0.001):
-    """BASELINE config 2 construction: N(0,1) with a few columns scaled by U[20,100]."""
+    """Benchmark configuration 2: N(0,1) with a few columns scaled by U[20,100]."""
     rng = np.random.default_rng(seed)
     x = rng.standard_normal((rows, cols)).astype(np.float32)
     ncol = max(1, int(round(outlier_frac * cols)))

@@ -43,7 +43,7 @@ def same_bytes(packed, want):
 
 
 CASES = [
-    # rows, cols, outlier, error, method, location          (BASELINE configs 1 and 2 first)
+    # rows, cols, outlier, error, method, location          (benchmark configurations 1 and 2 first)
     (1024, 1024, 0.0, 0.0, 11, 0),
     (4096, 4096, 0.01, 0.0, 10, 1),
     (512, 8192, 0.0, 0.0, 11, 1),
@@ -53,7 +53,7 @@ CASES = [
     (100, 200, 0.03, 0.02, 10, 1),          # blocks straddle rows, generic top-k
     (64, 1000, 0.01, 0.0, 11, 1),
     (33, 4096, 0.005, 0.01, 11, 1),
-    (192, 14336, 0.005, 0.0, 10, 1),        # row length of BASELINE configs[4] (k = 72): 8 warps per row
+    (192, 14336, 0.005, 0.0, 10, 1),        # row length of benchmark configuration 5 (k = 72): 8 warps per row
     (192, 14336, 0.005, 0.01, 11, 1),       # ... with error correction (k = 143)
     (128, 512, 0.0, 0.0, -1, 1),            # dense FP32 section
     (128, 512, 0.02, 0.0, -1, 0),

@@ -126,7 +126,7 @@ def test_svd_against_reference_cuda(lib, oracle_mod):
         ref.lib.ref_svd_release()
         ru, rs, rv = ru.cpu().numpy(), rs.cpu().numpy(), rv.cpu().numpy()
         e_ours, e_ref = rel_frob(a, (u * s) @ v.T), rel_frob(a, (ru * rs) @ rv.T)
-        # BASELINE north_star: reconstruction error within 1e-4 of the reference's
+        # the contract: reconstruction error within 1e-4 of the reference's
         assert abs(e_ours - e_ref) <= 1e-4, (e_ours, e_ref)
         # the reference's own S is not repeatable between calls (its random matrix advances), so only
         # the well-separated leading values can be compared: 1e-4 relative
