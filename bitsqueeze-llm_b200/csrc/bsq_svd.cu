@@ -505,6 +505,11 @@ __global__ void __launch_bounds__(1024) cholesky_inverse_blocked_kernel(const fl
 constexpr int kJacobiMaxK = 128;              // what the one-CTA kernel can hold
 constexpr int kJacobiSingleMaxK = 64;         // what it is used for: above, the cluster kernel is faster
 constexpr int kJacobiMaxSweeps = 30;
+// A sweep in which no visited pair had |cos(m_p, m_q)| above this is the last one: Jacobi converges quadratically,
+// so what such a sweep's rotations leave between the columns is of the order of the square of what it met
+// (<= 1e-8, below tol), and the sweep that would only confirm it (a full sweep's time for no rotation) is not run.
+// Pairs between tol and this bound are still rotated when they are met.
+constexpr float kJacobiLastSweepCos = 1.0e-4f;
 __host__ __device__ constexpr int jacobi_len(int k) { return k <= 64 ? 64 : 128; }
 __host__ __device__ constexpr size_t jacobi_smem_bytes(int k) {
     return ((size_t)2 * ((k + 1) & ~1) * jacobi_len(k) + 2 * (size_t)((k + 1) & ~1) + 64) * sizeof(float);
@@ -603,7 +608,7 @@ __global__ void __launch_bounds__(512) jacobi_svd_kernel(const float *__restrict
                     nrm[p] = fmaxf(alpha - t * g, 0.0f);
                     nrm[q] = beta + t * g;
                 }
-                rotated = rotated || sn != 0.0f;
+                rotated = rotated || g * g > kJacobiLastSweepCos * kJacobiLastSweepCos * alpha * beta;
             }
             __syncthreads();
         }
@@ -734,7 +739,7 @@ __global__ void __launch_bounds__(kJcLen / 2 * kLpp, 1) jacobi_svd_cluster_kerne
         return x;
     };
     // Exact squared norms of all columns (partial over this CTA's rows, exchanged, added in CTA order) and, on the
-    // same cluster barrier, the CTAs' votes: bit 0 = "rotated a pair in the last sweep", bit 1 = "a wait ran out".
+    // same cluster barrier, the CTAs' votes: bit 0 = "met a pair above kJacobiLastSweepCos in the last sweep", bit 1 = "a wait ran out".
     // Every CTA reads the same eight votes, so all of them leave the sweep loop in the same sweep whatever happened.
     // (The first of these barriers also makes the mbarriers' initialisation known to the whole cluster.)
     auto norms_and_votes = [&](int my_vote) {
@@ -863,7 +868,7 @@ __global__ void __launch_bounds__(kJcLen / 2 * kLpp, 1) jacobi_svd_cluster_kerne
                     nrm[p] = fmaxf(alpha - t * g, 0.0f);
                     nrm[q] = beta + t * g;
                 }
-                rotated = rotated || sn != 0.0f;
+                rotated = rotated || g * g > kJacobiLastSweepCos * kJacobiLastSweepCos * alpha * beta;
             }
             __syncthreads();                                  // this CTA's slices are rotated before the next round reads them
         }

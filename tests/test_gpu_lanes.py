@@ -90,7 +90,9 @@ def test_lane_host_and_device_objects_equal_public_call(pkg, lib, cfg):
         assert size.value == want.size and hdr.payload == d_packed.data_ptr() + 200
         back = d_packed[: size.value].cpu().numpy()
         assert np.array_equal(masked(back), masked(want))
-        assert pkg.load_packed(back) is not None or True
+        loaded = pkg.load_packed(back)                       # the device buffer's bytes are a loadable serialised object
+        assert loaded
+        lib.bsq_free(loaded)
         d_y = torch.zeros((rows, cols), dtype=torch.float32, device="cuda")
         assert lib.bsq_lane_decompress_begin(lane, C.byref(hdr), 1, d_y.data_ptr(), n) == 0
         assert lib.bsq_lane_decompress_end(lane) == 0
