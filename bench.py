@@ -796,7 +796,11 @@ def main():
     torch.cuda.empty_cache()
     sharded = None
     if world > 1 and not args.skip_extras:
-        sharded = row_sharded_leg(torch, dist, pkg, L, W, rank, world)
+        # a failure here must not cost the line: what the leg cannot do is reported inside its own object
+        try:
+            sharded = row_sharded_leg(torch, dist, pkg, L, W, rank, world)
+        except Exception as exc:                             # noqa: BLE001 (reported, not hidden)
+            sharded = {"error": "%s: %s" % (type(exc).__name__, exc)}
 
     if rank == 0:
         hbm_peak, bf16_peak, peak_kind = measured_peaks()
@@ -845,14 +849,22 @@ def main():
                          "timed": "CUDA events on the lane's stream around each product, one matrix in flight"},
             "clocks": clocks,
         }
+        if clocks and clocks.get("sm_mhz"):
+            # time x clock: comparable between runs whose sampled SM clocks differ (nothing sets the clocks)
+            line["clocks"]["ms_per_step_x_sm_ghz"] = ms_total / nsteps * clocks["sm_mhz"] / 1000.0
         if sharded is not None:
             line["row_sharded_svd"] = sharded
         if not args.skip_extras:
-            line["configs1_frontend"] = c2_frontend_leg(torch, pkg, L, W, hbm_peak)
+            def guarded(leg, *a):                             # a side measurement that fails is reported in its own object
+                try:
+                    return leg(*a)
+                except Exception as exc:                      # noqa: BLE001
+                    return {"error": "%s: %s" % (type(exc).__name__, exc)}
+            line["configs1_frontend"] = guarded(c2_frontend_leg, torch, pkg, L, W, hbm_peak)
             if world == 1:
                 if all_cpus:
                     os.sched_setaffinity(0, all_cpus)         # the CPU baseline runs on every core this process may use
-                line["cpu_baseline"] = cpu_nf4_baseline(W)
+                line["cpu_baseline"] = guarded(cpu_nf4_baseline, W)
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

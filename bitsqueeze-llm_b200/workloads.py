@@ -29,6 +29,7 @@ CONFIGS = {
 C5A_LAYERS = 32
 C5A_BASE_SEED = 5000
 C5B = dict(rows=65536, cols=4096, rank=128, niters=2, seed=77)
+SLICE_BAND = 2048          # rows per independently seeded band of a row-sliced matrix (lowrank_matrix)
 
 
 def c1_matrix(seed=1):
@@ -58,17 +59,18 @@ def lowrank_matrix(torch, rows, cols, seed, llama_like=False, components=512, no
     g2, _ = torch.linalg.qr(torch.randn(cols, components, device=device, generator=g, dtype=f64))
     sv = torch.arange(1, components + 1, device=device, dtype=f64) ** -1.0
     if row_slice is not None:
-        # the noise of a slice is drawn per 8192-row band with a seed of its own, so that every slicing of the same
-        # matrix into whole bands sees the same values
+        # the noise of a slice is drawn per band of SLICE_BAND rows with a seed of its own, so that every slicing of
+        # the same matrix into whole bands sees the same values (32768 rows over 8 ranks are 4096 rows each)
         first, count = row_slice
-        assert first % 8192 == 0 and count % 8192 == 0 and not llama_like
+        if first % SLICE_BAND or count % SLICE_BAND or count <= 0 or first + count > rows or llama_like:
+            raise ValueError("row_slice must be whole bands of %d rows inside the matrix (and not llama_like)" % SLICE_BAND)
         out = torch.empty(count, cols, device=device, dtype=torch.float32)
-        for b in range(count // 8192):
-            band = (first // 8192) + b
+        for b in range(count // SLICE_BAND):
+            band = (first // SLICE_BAND) + b
             gb = torch.Generator(device=device).manual_seed(int(seed) * 1000 + band)
-            rows_b = slice((first + b * 8192), (first + (b + 1) * 8192))
-            a = (g1[rows_b] * sv) @ g2.T + noise * torch.randn(8192, cols, device=device, generator=gb, dtype=f64)
-            out[b * 8192:(b + 1) * 8192] = a.float()
+            rows_b = slice((first + b * SLICE_BAND), (first + (b + 1) * SLICE_BAND))
+            a = (g1[rows_b] * sv) @ g2.T + noise * torch.randn(SLICE_BAND, cols, device=device, generator=gb, dtype=f64)
+            out[b * SLICE_BAND:(b + 1) * SLICE_BAND] = a.float()
         return out.contiguous()
     a = (g1 * sv) @ g2.T + noise * torch.randn(rows, cols, device=device, generator=g, dtype=f64)
     if llama_like:
