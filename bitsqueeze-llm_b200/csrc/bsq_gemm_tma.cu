@@ -60,6 +60,18 @@ __device__ __forceinline__ void tma_load_2d(void *dst_smem, const CUtensorMap *m
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Position in a ring of `n` stages and the parity of its current round.  Every role walks its rings with one of these:
+// a division and a remainder by the (run-time) ring length per stage were most of what the single threads that issue
+// the copies and the MMAs executed per stage.
+struct Ring {
+    int pos = 0, n;
+    unsigned par = 0;            // parity of the round `pos` is in
+    bool wrapped = false;        // the ring has been around at least once: the stage at `pos` has a previous use
+    __device__ __forceinline__ explicit Ring(int stages) : n(stages) {}
+    __device__ __forceinline__ void next() {
+        if (++pos == n) { pos = 0; par ^= 1u; wrapped = true; }
+    }
+};
 __device__ __forceinline__ void tc_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -165,21 +177,21 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
         // ---- A producer: one box per slot, as far ahead as the ring allows ----
         if (lane == 0) {
             int ca = 0;                                                  // slots filled so far, over all tiles
+            Ring ra(A_KMAJOR ? NR : NRAW);
             for (int i = 0; i < walk.count && ok; ++i) {
                 int mt, nt, z;
                 walk.at(i, &mt, &nt, &z);
                 const int k_begin = z * g.k_per_split, k_end = min(g.K, k_begin + g.k_per_split);
                 const int chunks_a = (k_end - k_begin + KS - 1) / KS;
-                for (int c = 0; c < chunks_a; ++c, ++ca) {
+                for (int c = 0; c < chunks_a; ++c, ++ca, ra.next()) {
+                    const int s = ra.pos;
                     if (A_KMAJOR) {
-                        const int s = ca % NR;
-                        if (ca >= NR) ok = mbar_wait_bounded(&bars.empty_a[s], (unsigned)(ca / NR - 1) & 1u, status);
+                        if (ra.wrapped) ok = mbar_wait_bounded(&bars.empty_a[s], ra.par ^ 1u, status);
                         if (!ok) break;
                         mbar_expect_tx(&bars.full_a[s], A_HALF);
                         tma_load_2d(a_slots + (size_t)s * A_SLOT, &tmap_a, k_begin + c * KS, mt * TM, &bars.full_a[s]);
                     } else {
-                        const int s = ca % NRAW;
-                        if (ca >= NRAW) ok = mbar_wait_bounded(&bars.raw_empty[s], (unsigned)(ca / NRAW - 1) & 1u, status);
+                        if (ra.wrapped) ok = mbar_wait_bounded(&bars.raw_empty[s], ra.par ^ 1u, status);
                         if (!ok) break;
                         mbar_expect_tx(&bars.raw_full[s], RAW_SLOT);
 #pragma unroll
@@ -201,6 +213,7 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
         // ---- B producer: the images of the tile's columns, one bulk copy each ----
         if (lane == 0) {
             int jb = 0;
+            Ring rb(NB);
             for (int i = 0; i < walk.count && ok; ++i) {
                 int mt, nt, z;
                 walk.at(i, &mt, &nt, &z);
@@ -209,9 +222,9 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                 const int N = min(g.n_tile, g.N - nt * g.n_tile);
                 const unsigned b_bytes = 2u * image_half_units(N) * 16u;
                 const float4 *image = g.b_image + ((size_t)nt * chunks_total + k_begin / TK) * image_units(g.n_tile);
-                for (int j = 0; j < chunks_b; ++j, ++jb) {
-                    const int sb = jb % NB;
-                    if (jb >= NB) ok = mbar_wait_bounded(&bars.empty_b[sb], (unsigned)(jb / NB - 1) & 1u, status);
+                for (int j = 0; j < chunks_b; ++j, ++jb, rb.next()) {
+                    const int sb = rb.pos;
+                    if (rb.wrapped) ok = mbar_wait_bounded(&bars.empty_b[sb], rb.par ^ 1u, status);
                     if (!ok) break;
                     mbar_expect_tx(&bars.full_b[sb], b_bytes);
                     bulk_g2s(b_slots + (size_t)sb * b_stride, image + (size_t)j * image_units(g.n_tile), b_bytes, &bars.full_b[sb]);
@@ -225,8 +238,8 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
     } else if (warp == 1) {
         // ---- MMA issuer ----
         if (lane == 0) {
-            int ca = 0, jb = 0;
-            for (int i = 0; i < walk.count && ok; ++i) {
+            Ring ra(NR), rb(NB), rs(acc_sets);
+            for (int i = 0; i < walk.count && ok; ++i, rs.next()) {
                 int mt, nt, z;
                 walk.at(i, &mt, &nt, &z);
                 const int k_begin = z * g.k_per_split, k_end = min(g.K, k_begin + g.k_per_split);
@@ -236,23 +249,23 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                 // FP32 accumulate, TF32 x TF32, both operands K-major, N >> 3, M >> 4
                 const unsigned idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned)(N >> 3) << 17) | ((unsigned)(TM >> 4) << 24);
                 const unsigned b_kstep = 2u * (unsigned)N;              // units from one 8-wide k-step of an image to the next
-                const int set = i % acc_sets;
+                const int set = rs.pos;
                 const unsigned acc = tmem_d + (unsigned)set * 2u * acc_cols;
                 // the epilogue must have read this accumulator set's previous tile out
-                if (i >= acc_sets) ok = mbar_wait_bounded(&bars.acc_empty[set], (unsigned)(i / acc_sets - 1) & 1u, status);
+                if (rs.wrapped) ok = mbar_wait_bounded(&bars.acc_empty[set], rs.par ^ 1u, status);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                for (int c = 0; c < chunks_a && ok; ++c, ++ca) {
-                    const int s = ca % NR;
-                    ok = mbar_wait_bounded(&bars.ready_a[s], (unsigned)(ca / NR) & 1u, status);
+                for (int c = 0; c < chunks_a && ok; ++c, ra.next()) {
+                    const int s = ra.pos;
+                    ok = mbar_wait_bounded(&bars.ready_a[s], ra.par, status);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const unsigned a_addr = smem_u32(a_slots + (size_t)s * A_SLOT);
                     const uint64_t da_hi = smem_desc_sw128(a_addr), da_lo = smem_desc_sw128(a_addr + A_HALF);
                     for (int h = 0; h < 2 && ok; ++h) {
                         if (2 * c + h >= chunks_b) break;                // K ends inside this slot: its second half is zeros
-                        const int sb = jb % NB;
-                        ok = mbar_wait_bounded(&bars.full_b[sb], (unsigned)(jb / NB) & 1u, status);
+                        const int sb = rb.pos;
+                        ok = mbar_wait_bounded(&bars.full_b[sb], rb.par, status);
                         if (!ok) break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint64_t db0 = smem_desc(smem_u32(b_slots + (size_t)sb * b_stride), (unsigned)N * 16u, 128u);
@@ -266,7 +279,7 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                             mma_tf32(acc + acc_cols, dah, dbl, idesc, true);
                         }
                         tc_commit(&bars.empty_b[sb]);
-                        ++jb;
+                        rb.next();
                     }
                     if (ok) tc_commit(&bars.empty_a[s]);
                 }
@@ -277,21 +290,21 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
     } else if (warp < 7) {
         // ---- transform: hi in place, lo behind it ----
         const int t = tid - 3 * 32;
-        int ca = 0;
+        Ring ra(NR), rr(A_KMAJOR ? 1 : NRAW);
         for (int i = 0; i < walk.count && ok; ++i) {
             int mt, nt, z;
             walk.at(i, &mt, &nt, &z);
             const int k_begin = z * g.k_per_split, k_end = min(g.K, k_begin + g.k_per_split);
             const int chunks_a = (k_end - k_begin + KS - 1) / KS;
-            for (int c = 0; c < chunks_a; ++c, ++ca) {
-                const int s = ca % NR;
+            for (int c = 0; c < chunks_a; ++c, ra.next(), rr.next()) {
+                const int s = ra.pos;
                 float4 *hi = reinterpret_cast<float4 *>(a_slots + (size_t)s * A_SLOT);
                 float4 *lo = hi + A_HALF / 16;
                 if (!A_KMAJOR) {
-                    const int sr = ca % NRAW;
-                    ok = mbar_wait_bounded(&bars.raw_full[sr], (unsigned)(ca / NRAW) & 1u, status);
+                    const int sr = rr.pos;
+                    ok = mbar_wait_bounded(&bars.raw_full[sr], rr.par, status);
                     // the MMAs that read this operand stage NR slots ago must be done with it
-                    if (ok && ca >= NR) ok = mbar_wait_bounded(&bars.empty_a[s], (unsigned)(ca / NR - 1) & 1u, status);
+                    if (ok && ra.wrapped) ok = mbar_wait_bounded(&bars.empty_a[s], ra.par ^ 1u, status);
                     if (!ok) break;
                     // thread t owns row t of the slot: box t / 32, float t % 32 of every k
                     const float *box = reinterpret_cast<const float *>(raw_slots + (size_t)sr * RAW_SLOT + (t >> 5) * RAW_BOX);
@@ -318,22 +331,20 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                     mbar_arrive(&bars.ready_a[s]);
                     continue;
                 }
-                ok = mbar_wait_bounded(&bars.full_a[s], (unsigned)(ca / NR) & 1u, status);
+                ok = mbar_wait_bounded(&bars.full_a[s], ra.par, status);
                 if (!ok) break;
                 float4 v[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] = hi[t + XF * j];
                 if (g.kscale) {
-                    // opA(i, kk) *= kscale[kk]: unit u of row r holds the 4 k of logical unit u ^ (r & 7)
-                    const int k0 = k_begin + c * KS;
+                    // opA(i, kk) *= kscale[kk]: unit u of row r holds the 4 k of logical unit u ^ (r & 7).  A thread's
+                    // eight units (e = t + 128 j: row (t >> 3) + 16 j, position t & 7) are the same logical unit of
+                    // eight rows, so the four factors are fetched once per slot.
+                    const int kk = k_begin + c * KS + (((t & 7) ^ ((t >> 3) & 7)) << 2);
+                    const float f0 = kk < k_end ? g.kscale[kk] : 0.f, f1 = kk + 1 < k_end ? g.kscale[kk + 1] : 0.f;
+                    const float f2 = kk + 2 < k_end ? g.kscale[kk + 2] : 0.f, f3 = kk + 3 < k_end ? g.kscale[kk + 3] : 0.f;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int e = t + XF * j, r = e >> 3, unit = (e & 7) ^ (r & 7);
-                        const int kk = k0 + unit * 4;
-                        const float f0 = kk < k_end ? g.kscale[kk] : 0.f, f1 = kk + 1 < k_end ? g.kscale[kk + 1] : 0.f;
-                        const float f2 = kk + 2 < k_end ? g.kscale[kk + 2] : 0.f, f3 = kk + 3 < k_end ? g.kscale[kk + 3] : 0.f;
-                        v[j].x *= f0; v[j].y *= f1; v[j].z *= f2; v[j].w *= f3;
-                    }
+                    for (int j = 0; j < 8; ++j) { v[j].x *= f0; v[j].y *= f1; v[j].z *= f2; v[j].w *= f3; }
                 }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) split_store(v[j], hi + t + XF * j, lo + t + XF * j);
@@ -346,12 +357,13 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
         // ---- epilogue: this thread's accumulator row of every tile, 16 columns at a time ----
         const int quarter = warp & 3;                                    // the tensor-memory lanes this warp may read
         bool any = false;
-        for (int i = 0; i < walk.count && ok; ++i) {
+        Ring rs(acc_sets);
+        for (int i = 0; i < walk.count && ok; ++i, rs.next()) {
             int mt, nt, z;
             walk.at(i, &mt, &nt, &z);
             const int n0 = nt * g.n_tile, N = min(g.n_tile, g.N - n0);
             const int row = mt * TM + quarter * 32 + lane;
-            const int set = i % acc_sets;
+            const int set = rs.pos;
             float *C = g.C + (long)z * g.split_stride;
             // A full 128-column tile with a minuend: the thread's whole row segment of the minuend is asked for before
             // the wait for the accumulators, so that its HBM latency passes while the tensor core still works on the
@@ -363,7 +375,7 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
 #pragma unroll
                 for (int j = 0; j < 32; ++j) mn_pre[j] = mn[j];
             }
-            ok = mbar_wait_bounded(&bars.acc_full[set], (unsigned)(i / acc_sets) & 1u, status);
+            ok = mbar_wait_bounded(&bars.acc_full[set], rs.par, status);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (pre) {
