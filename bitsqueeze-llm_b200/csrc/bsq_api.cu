@@ -325,7 +325,7 @@ bool setup_runtime(Runtime &rt, bool compress, uint16_t rows, uint16_t cols, flo
         const size_t r = (size_t)rt.rank;
         if (!rt.u.alloc((size_t)rows * r * 4) || !rt.s.alloc(r * 4) || !rt.v.alloc((size_t)cols * r * 4)) return false;
         if (!compress || ke > 0) {                      // the reconstruction runs on decompress and for the error stage
-            rt.recon_ws_bytes = reconstruct_workspace_bytes(cols, rt.rank);
+            rt.recon_ws_bytes = reconstruct_workspace_bytes(rows, cols, rt.rank);
             if (rt.recon_ws_bytes && !rt.recon_ws.alloc(rt.recon_ws_bytes)) return false;
         }
         if (compress) {

@@ -203,6 +203,15 @@ int b_image_mode() {
     return mode;
 }
 
+// BSQ_GEMM_AIMAGE=0: the persistent product splits A in the kernel (transform warps) instead of beforehand.
+bool a_image_enabled() {
+    static const bool on = [] {
+        const char *e = std::getenv("BSQ_GEMM_AIMAGE");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 // BSQ_GEMM_TC=0 keeps every product on the FP32 pipes (for A/B comparisons of the two kernels).
 bool tensor_cores_enabled() {
     static const bool on = [] {
@@ -271,6 +280,13 @@ cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, c
                 // by a persistent grid
                 t.n_tile = 128;
                 t.persistent = true;
+                // a small A read again by every column tile: split once beforehand too, when the workspace has the room
+                // (in front of B's images; a persistent product has no K split and so no partial results there)
+                const size_t a_room = (gemm_tc_a_image_bytes(M, K) + 127) & ~(size_t)127;
+                if (a_kmajor && K % 4 == 0 && a_image_enabled() && workspace_bytes >= a_room && reinterpret_cast<uintptr_t>(workspace) % 128 == 0) {
+                    t.a_image = workspace;
+                    t.a_image_rows = (M + 127) / 128 * 128;
+                }
             }
         }
         const int slots = (t.use_tma ? 1 : with_image ? gemm_tc_image_ctas_per_sm(t.n_tile) : (t.n_tile <= 128 ? 2 : 1)) * sm_count;

@@ -25,6 +25,10 @@ struct GemmArgs {
     int raw_stages;            // TMA-fed kernel, A contiguous along M: slots of boxes as they come from memory
     bool use_tma;              // with b_image: the kernel that brings A in by TMA (bsq_gemm_tma.cu)
     bool persistent;           // with use_tma, no K split: one CTA per SM walks over all tiles (wide products)
+    float *a_image;            // with persistent and A contiguous along K, nullable: room for A (times kscale) split beforehand into
+                               // two row-major a_image_rows x K matrices, hi then lo (gemm_tc_a_image_bytes): a small A that every
+                               // column tile reads again then comes in by TMA ready for the tensor core, and nobody splits in the kernel
+    int a_image_rows;          // M rounded up to the tile height
     int sm_count;
 };
 
@@ -35,6 +39,7 @@ bool gemm_tc_eligible(const GemmArgs &g, bool a_kmajor, bool b_kmajor);
 // With g.b_image set, B is first split into per-chunk hi / lo images there (one small kernel) and the product kernel
 // fetches them by bulk copies; gemm_tc_image_bytes is the room that takes.
 size_t gemm_tc_image_bytes(int N, int n_tile, int K);
+size_t gemm_tc_a_image_bytes(int M, int K);
 int gemm_tc_image_ctas_per_sm(int n_tile);
 void gemm_tc_image_rings(int n_tile, int *sa, int *nb);
 cudaError_t gemm_tc_launch(const GemmArgs &g, bool a_kmajor, bool b_kmajor, unsigned *status, cudaStream_t stream);

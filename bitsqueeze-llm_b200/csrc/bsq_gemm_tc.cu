@@ -485,6 +485,23 @@ __global__ void __launch_bounds__(256) presplit_b_kernel(const float *__restrict
     split_store(make_float4(v[0], v[1], v[2], v[3]), img + u, img + image_half_units(Nt) + u);
 }
 
+// A (contiguous along K, times kscale) split into two row-major rows_pad x K matrices, hi then lo, four k per thread;
+// rows past M are zeros.  The values are those the product kernel's transform warps would make of the same A.
+__global__ void __launch_bounds__(256) presplit_a_kernel(const float *__restrict__ A, long lda, int M, int K, const float *__restrict__ kscale,
+                                                         float *__restrict__ image, int rows_pad) {
+    const int k4 = K / 4;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)rows_pad * k4) return;
+    const int m = (int)(idx / k4), k = (int)(idx % k4) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (m < M) {
+        v = *reinterpret_cast<const float4 *>(A + (long)m * lda + k);
+        if (kscale) { v.x *= kscale[k]; v.y *= kscale[k + 1]; v.z *= kscale[k + 2]; v.w *= kscale[k + 3]; }
+    }
+    float4 *hi = reinterpret_cast<float4 *>(image + (long)m * K + k);
+    split_store(v, hi, hi + (long)rows_pad * k4);
+}
+
 template <bool A_KMAJOR, int NMAX>
 __global__ void __launch_bounds__(NT2, NMAX <= 128 ? 2 : 1) gemm_tc_image_kernel(GemmArgs g, unsigned *status) {
     // chunks of A in flight in registers per thread: what is in flight per SM is what bounds these products (the
@@ -671,6 +688,11 @@ cudaError_t launch_image(const GemmArgs &g, bool b_kmajor, unsigned *status, cud
     else presplit_b_kernel<false><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image);
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return err;
+    if (g.use_tma && g.a_image) {
+        const long quads = (long)g.a_image_rows * (g.K / 4);
+        presplit_a_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, stream>>>(g.A, g.lda, g.M, g.K, g.kscale, g.a_image, g.a_image_rows);
+        if ((err = cudaGetLastError()) != cudaSuccess) return err;
+    }
     if (g.use_tma) return gemm_tc_tma_launch(g, AK, status, stream);
     const size_t smem = tc_image_smem_bytes(g.n_tile, g.a_stages, g.b_stages);
     err = cudaFuncSetAttribute(gemm_tc_image_kernel<AK, NMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -691,6 +713,8 @@ int gemm_tc_image_ctas_per_sm(int n_tile) {
     return by_smem < by_tmem ? (by_smem < 1 ? 1 : by_smem) : by_tmem;
 }
 void gemm_tc_image_rings(int n_tile, int *sa, int *nb) { tc_image_rings(n_tile, sa, nb); }
+
+size_t gemm_tc_a_image_bytes(int M, int K) { return (size_t)2 * ((M + TM - 1) / TM * TM) * K * sizeof(float); }
 
 size_t gemm_tc_image_bytes(int N, int n_tile, int K) {
     return (size_t)((N + n_tile - 1) / n_tile) * ((K + TK - 1) / TK) * image_units(n_tile) * 16;

@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
     unsigned char *base = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);      // the swizzle wants 1024-byte aligned slots
     const int NR = g.a_stages, NB = g.b_stages, NRAW = A_KMAJOR ? 0 : g.raw_stages;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool a_img = A_KMAJOR && g.a_image != nullptr;           // A split beforehand: both halves of a slot come in by TMA
     const unsigned b_stride = 2u * image_half_units(g.n_tile) * 16u;
     unsigned char *raw_slots = base;
     unsigned char *a_slots = raw_slots + (size_t)NRAW * RAW_SLOT;
@@ -188,8 +189,14 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                     if (A_KMAJOR) {
                         if (ra.wrapped) ok = mbar_wait_bounded(&bars.empty_a[s], ra.par ^ 1u, status);
                         if (!ok) break;
-                        mbar_expect_tx(&bars.full_a[s], A_HALF);
-                        tma_load_2d(a_slots + (size_t)s * A_SLOT, &tmap_a, k_begin + c * KS, mt * TM, &bars.full_a[s]);
+                        if (a_img) {                                     // hi and lo of the slot, split beforehand
+                            mbar_expect_tx(&bars.full_a[s], A_SLOT);
+                            tma_load_2d(a_slots + (size_t)s * A_SLOT, &tmap_a, k_begin + c * KS, mt * TM, &bars.full_a[s]);
+                            tma_load_2d(a_slots + (size_t)s * A_SLOT + A_HALF, &tmap_a, k_begin + c * KS, g.a_image_rows + mt * TM, &bars.full_a[s]);
+                        } else {
+                            mbar_expect_tx(&bars.full_a[s], A_HALF);
+                            tma_load_2d(a_slots + (size_t)s * A_SLOT, &tmap_a, k_begin + c * KS, mt * TM, &bars.full_a[s]);
+                        }
                     } else {
                         if (ra.wrapped) ok = mbar_wait_bounded(&bars.raw_empty[s], ra.par ^ 1u, status);
                         if (!ok) break;
@@ -257,7 +264,7 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 for (int c = 0; c < chunks_a && ok; ++c, ra.next()) {
                     const int s = ra.pos;
-                    ok = mbar_wait_bounded(&bars.ready_a[s], ra.par, status);
+                    ok = mbar_wait_bounded(a_img ? &bars.full_a[s] : &bars.ready_a[s], ra.par, status);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const unsigned a_addr = smem_u32(a_slots + (size_t)s * A_SLOT);
@@ -288,10 +295,10 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
             if (!ok) atomicOr(&bars.failed, 1u);
         }
     } else if (warp < 7) {
-        // ---- transform: hi in place, lo behind it ----
+        // ---- transform: hi in place, lo behind it (nothing to do when A was split beforehand) ----
         const int t = tid - 3 * 32;
         Ring ra(NR), rr(A_KMAJOR ? 1 : NRAW);
-        for (int i = 0; i < walk.count && ok; ++i) {
+        for (int i = 0; i < (a_img ? 0 : walk.count) && ok; ++i) {
             int mt, nt, z;
             walk.at(i, &mt, &nt, &z);
             const int k_begin = z * g.k_per_split, k_end = min(g.K, k_begin + g.k_per_split);
@@ -514,12 +521,13 @@ bool gemm_tc_tma_usable(const GemmArgs &g, bool a_kmajor) {
 cudaError_t gemm_tc_tma_launch(const GemmArgs &g, bool a_kmajor, unsigned *status, cudaStream_t stream) {
     CUtensorMap map;
     // innermost dimension first: K (then M) for an A contiguous along K, M (then K) otherwise
-    const cuuint64_t dims[2] = {(cuuint64_t)(a_kmajor ? g.K : g.M), (cuuint64_t)(a_kmajor ? g.M : g.K)};
-    const cuuint64_t strides[1] = {(cuuint64_t)g.lda * sizeof(float)};
+    const bool a_img = a_kmajor && g.a_image != nullptr;         // the map then covers the hi and lo matrices, one above the other
+    const cuuint64_t dims[2] = {(cuuint64_t)(a_kmajor ? g.K : g.M), (cuuint64_t)(a_img ? 2 * g.a_image_rows : (a_kmajor ? g.M : g.K))};
+    const cuuint64_t strides[1] = {(cuuint64_t)(a_img ? g.K : g.lda) * sizeof(float)};
     const cuuint32_t box[2] = {32, (cuuint32_t)(a_kmajor ? TM : KS)};
     const cuuint32_t estr[2] = {1, 1};
     static const int l2 = [] { const char *e = std::getenv("BSQ_TMA_L2"); return e ? atoi(e) : 128; }();
-    if (encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(g.A), dims, strides, box, estr,
+    if (encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, a_img ? g.a_image : const_cast<float *>(g.A), dims, strides, box, estr,
                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                        l2 == 256 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : (l2 == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_128B),
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)

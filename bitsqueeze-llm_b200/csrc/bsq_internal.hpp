@@ -107,9 +107,9 @@ cudaError_t svd_workspace_finish(SvdWorkspace *ws, cudaStream_t stream);
 // OR 1 into *d_flag when some |difference| > FLT_EPSILON.
 // d_status (nullable): device word that receives kStatusBarrierTimeout if a bounded wait of the product kernel gives up
 // (the output is then incomplete).
-// d_workspace (nullable, reconstruct_workspace_bytes): room for V split once into the tensor cores' operand format,
-// shared by all row tiles; without it every tile splits its piece of V itself.
-size_t reconstruct_workspace_bytes(int n, int k);
+// d_workspace (nullable, reconstruct_workspace_bytes, 128-byte aligned): room for V and U diag(S) split once into the
+// tensor cores' operand format, shared by all tiles; without it every tile splits its pieces itself.
+size_t reconstruct_workspace_bytes(int m, int n, int k);
 cudaError_t reconstruct_lowrank(const float *d_U, const float *d_S, const float *d_V, int m, int n, int k,
                                 const float *d_minuend, float *d_out, unsigned *d_flag, unsigned *d_status, float *d_workspace,
                                 size_t workspace_bytes, int sm_count, cudaStream_t stream);

@@ -1232,7 +1232,10 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
                 ws->sm_count, st);
 }
 
-size_t reconstruct_workspace_bytes(int n, int k) { return n > 256 ? gemm_tc_image_bytes(n, 256, k) + 512 : 0; }
+size_t reconstruct_workspace_bytes(int m, int n, int k) {
+    // V's images, and in front of them U diag(S) split beforehand (the persistent product of bsq_gemm.cu)
+    return n > 256 ? gemm_tc_image_bytes(n, 256, k) + ((gemm_tc_a_image_bytes(m, k) + 127) & ~(size_t)127) + 1024 : 0;
+}
 
 cudaError_t reconstruct_lowrank(const float *d_U, const float *d_S, const float *d_V, int m, int n, int k,
                                 const float *d_minuend, float *d_out, unsigned *d_flag, unsigned *d_status, float *d_workspace,
