@@ -212,6 +212,15 @@ bool a_image_enabled() {
     return on;
 }
 
+// BSQ_GEMM_WIDE=0: the persistent product keeps 128-column tiles (two accumulators per tile) when A is split beforehand.
+bool wide_tiles_enabled() {
+    static const bool on = [] {
+        const char *e = std::getenv("BSQ_GEMM_WIDE");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 // BSQ_GEMM_TC=0 keeps every product on the FP32 pipes (for A/B comparisons of the two kernels).
 bool tensor_cores_enabled() {
     static const bool on = [] {
@@ -286,6 +295,10 @@ cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, c
                 if (a_kmajor && K % 4 == 0 && a_image_enabled() && workspace_bytes >= a_room && reinterpret_cast<uintptr_t>(workspace) % 128 == 0) {
                     t.a_image = workspace;
                     t.a_image_rows = (M + 127) / 128 * 128;
+                    if (wide_tiles_enabled()) {
+                        t.n_tile = 256;                                 // (B's images were given room for 256-column tiles above)
+                        t.wide_tiles = true;
+                    }
                 }
             }
         }

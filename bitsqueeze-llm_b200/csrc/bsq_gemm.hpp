@@ -29,6 +29,10 @@ struct GemmArgs {
                                // two row-major a_image_rows x K matrices, hi then lo (gemm_tc_a_image_bytes): a small A that every
                                // column tile reads again then comes in by TMA ready for the tensor core, and nobody splits in the kernel
     int a_image_rows;          // M rounded up to the tile height
+    bool wide_tiles;           // with a_image: 256-column tiles whose three products share one accumulator (two accumulator sets
+                               // then fit tensor memory), their epilogue shared by the warps that have nothing to split: per
+                               // column of C half as many barrier waits, descriptors and commits for the one thread that issues
+                               // the MMAs, which is what bounds a product with a short K
     int sm_count;
 };
 

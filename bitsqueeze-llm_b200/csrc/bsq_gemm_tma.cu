@@ -137,8 +137,11 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
     TmaBars &bars = *reinterpret_cast<TmaBars *>(b_slots + (size_t)NB * b_stride);
     // accumulator columns of one set (hi*hi chain and, acc_cols further on, the cross terms), and how many sets
     const unsigned acc_cols = g.n_tile <= 16 ? 16u : (g.n_tile <= 32 ? 32u : (g.n_tile <= 64 ? 64u : (g.n_tile <= 128 ? 128u : 256u)));
-    const int acc_sets = (g.persistent && acc_cols <= 128u) ? 2 : 1;
-    const unsigned tmem_cols = 2u * acc_cols * (unsigned)acc_sets;
+    const bool one_acc = a_img && g.wide_tiles;                    // the cross terms go into the hi * hi accumulator
+    const unsigned acc_stride = one_acc ? acc_cols : 2u * acc_cols;  // tensor-memory columns of one set
+    const int acc_sets = (g.persistent && acc_stride <= 256u) ? 2 : 1;
+    const unsigned tmem_cols = acc_stride * (unsigned)acc_sets;
+    const int epi_groups = one_acc ? 2 : 1;                        // wide tiles: the transform warps take the tile's second 128 columns
     const TileWalk walk(g);
     const int chunks_total = (g.K + TK - 1) / TK;
 
@@ -158,7 +161,7 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bars.acc_full[i], 1);
-            mbar_init(&bars.acc_empty[i], XF);
+            mbar_init(&bars.acc_empty[i], XF * epi_groups);
         }
         bars.failed = 0;
         mbar_fence_init();
@@ -257,7 +260,7 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                 const unsigned idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned)(N >> 3) << 17) | ((unsigned)(TM >> 4) << 24);
                 const unsigned b_kstep = 2u * (unsigned)N;              // units from one 8-wide k-step of an image to the next
                 const int set = rs.pos;
-                const unsigned acc = tmem_d + (unsigned)set * 2u * acc_cols;
+                const unsigned acc = tmem_d + (unsigned)set * acc_stride, acc_x = one_acc ? acc : acc + acc_cols;
                 // the epilogue must have read this accumulator set's previous tile out
                 if (rs.wrapped) ok = mbar_wait_bounded(&bars.acc_empty[set], rs.par ^ 1u, status);
                 if (!ok) break;
@@ -282,8 +285,8 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                             const uint64_t dah = da_hi + (uint64_t)(kk * 2), dal = da_lo + (uint64_t)(kk * 2);
                             const uint64_t dbh = db0 + (uint64_t)(ks * b_kstep), dbl = dbh + b_units;
                             mma_tf32(acc, dah, dbh, idesc, c > 0 || kk > 0);
-                            mma_tf32(acc + acc_cols, dal, dbh, idesc, c > 0 || kk > 0);
-                            mma_tf32(acc + acc_cols, dah, dbl, idesc, true);
+                            mma_tf32(acc_x, dal, dbh, idesc, one_acc || c > 0 || kk > 0);
+                            mma_tf32(acc_x, dah, dbl, idesc, true);
                         }
                         tc_commit(&bars.empty_b[sb]);
                         rb.next();
@@ -294,7 +297,7 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
             }
             if (!ok) atomicOr(&bars.failed, 1u);
         }
-    } else if (warp < 7) {
+    } else if (warp < 7 && !one_acc) {
         // ---- transform: hi in place, lo behind it (nothing to do when A was split beforehand) ----
         const int t = tid - 3 * 32;
         Ring ra(NR), rr(A_KMAJOR ? 1 : NRAW);
@@ -363,6 +366,7 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
     } else {
         // ---- epilogue: this thread's accumulator row of every tile, 16 columns at a time ----
         const int quarter = warp & 3;                                    // the tensor-memory lanes this warp may read
+        const int cb = (one_acc && warp < 7) ? 128 : 0;                  // wide tiles: first column of this warp's half of the tile
         bool any = false;
         Ring rs(acc_sets);
         for (int i = 0; i < walk.count && ok; ++i, rs.next()) {
@@ -375,10 +379,11 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
             // A full 128-column tile with a minuend: the thread's whole row segment of the minuend is asked for before
             // the wait for the accumulators, so that its HBM latency passes while the tensor core still works on the
             // tile (fetched 16 columns at a time inside the loop below, every step would wait for memory on its own).
-            const bool pre = g.minuend != nullptr && N == 128 && row < g.M;
+            const int ce = one_acc ? min(N, cb + 128) : N;                // this thread's columns of the tile: cb .. ce - 1
+            const bool pre = g.minuend != nullptr && ce - cb == 128 && row < g.M;
             float4 mn_pre[32];
             if (pre) {
-                const float4 *mn = reinterpret_cast<const float4 *>(g.minuend + (long)row * g.ldm + n0);
+                const float4 *mn = reinterpret_cast<const float4 *>(g.minuend + (long)row * g.ldm + n0 + cb);
 #pragma unroll
                 for (int j = 0; j < 32; ++j) mn_pre[j] = mn[j];
             }
@@ -386,14 +391,18 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (pre) {
-                float4 *dst = reinterpret_cast<float4 *>(C + (long)row * g.ldc + n0);
+                float4 *dst = reinterpret_cast<float4 *>(C + (long)row * g.ldc + n0 + cb);
 #pragma unroll
                 for (int s16 = 0; s16 < 8; ++s16) {
                     unsigned r[16], q[16];
-                    const unsigned taddr = tmem_d + (unsigned)set * 2u * acc_cols + ((unsigned)(quarter * 32) << 16) + (unsigned)(s16 * 16);
+                    const unsigned taddr = tmem_d + (unsigned)set * acc_stride + ((unsigned)(quarter * 32) << 16) + (unsigned)(cb + s16 * 16);
                     tmem_ld16(taddr, r);
-                    tmem_ld16(taddr + acc_cols, q);
+                    if (!one_acc) tmem_ld16(taddr + acc_cols, q);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (one_acc) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) q[j] = 0x80000000u;    // (-0.0f: the sum below leaves r as it is, bit for bit)
+                    }
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const float4 m4 = mn_pre[s16 * 4 + j];
@@ -408,14 +417,16 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                     }
                 }
             } else
-            for (int c0 = 0; c0 < N; c0 += 16) {
+            for (int c0 = cb; c0 < ce; c0 += 16) {
                 unsigned r[16], q[16];
-                const unsigned taddr = tmem_d + (unsigned)set * 2u * acc_cols + ((unsigned)(quarter * 32) << 16) + (unsigned)c0;
+                const unsigned taddr = tmem_d + (unsigned)set * acc_stride + ((unsigned)(quarter * 32) << 16) + (unsigned)c0;
                 tmem_ld16(taddr, r);
-                tmem_ld16(taddr + acc_cols, q);
+                if (!one_acc) tmem_ld16(taddr + acc_cols, q);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (!one_acc) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(q[j])));
+                    for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(q[j])));
+                }
                 if (row < g.M) {
                     float4 *dst = reinterpret_cast<float4 *>(C + (long)row * g.ldc + n0 + c0);
                     if (g.minuend) {
