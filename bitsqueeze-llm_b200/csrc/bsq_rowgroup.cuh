@@ -19,6 +19,10 @@
 
 namespace bsq {
 
+constexpr unsigned kFlagSpecial = 1u;      // GroupCtl::flags: the row holds Inf or NaN
+constexpr unsigned kFlagSlow = 2u;         //                  some block of the row takes the literal scan
+constexpr unsigned kFlagTie = 4u;          //                  two candidates share |x|: rank on the full composite
+
 // control words of one group
 struct GroupCtl {
     unsigned long long bar;        // mbarrier of the row copy
@@ -102,7 +106,10 @@ __device__ __forceinline__ void expand_hits(const RowGroup<G> &g, GroupCtl &c, c
         for (int q = 0; q < 4; ++q) {
             if (fabsf(v[q]) >= bound) {
                 const unsigned pos = atomicAdd(&c.count, 1u);
-                if (pos < (unsigned)kCandCap) c.cand[pos] = topk_composite(v[q], i * 4 + q);
+                if (pos < (unsigned)kCandCap) {
+                    c.key[pos] = __float_as_uint(v[q]) & 0x7fffffffu;
+                    c.cand[pos] = topk_composite(v[q], i * 4 + q);
+                }
             }
         }
     }
@@ -136,6 +143,51 @@ __device__ __forceinline__ void group_rank_emit(const RowGroup<G> &g, GroupCtl &
                 if (rank == k - 1) c.kth_bits = __float_as_uint(v) & 0x7fffffffu;
                 if (zero_selected) row[col] = 0.0f;
             }
+        }
+    }
+    g.sync();
+}
+
+// The same for candidates whose |x| bits are also in c.key[] (finite values, zeros beyond `count` up to a multiple of
+// four): ranks come from 32-bit compares, four keys per load, a quarter of the instructions of the 64-bit count above
+// (which bounded the error-correction pass: 143 of 14336 per row means ~200 candidates, 200 x 200 compares).  Two
+// candidates of equal |x| would get the same rank, which the `seen` bits catch: then everybody ranks on the full
+// composite (column ascending breaks the tie).  c.hist[] keeps the ranks; c.seen[] and kFlagTie in c.flags must be
+// clear on entry.  Ends with a group sync.
+template <int G>
+__device__ __forceinline__ void group_rank_emit_keys(const RowGroup<G> &g, GroupCtl &c, float *row, unsigned count, unsigned k,
+                                                     uint16_t *out_idx, float *out_val, bool zero_selected) {
+    constexpr unsigned L = RowGroup<G>::L;
+    const uint4 *key4 = reinterpret_cast<const uint4 *>(c.key);
+    const unsigned n4 = (count + 3) >> 2;
+    for (unsigned j = g.lane; j < count; j += L) {
+        const unsigned m = c.key[j];
+        unsigned r = 0;
+#pragma unroll 4
+        for (unsigned i = 0; i < n4; ++i) {
+            const uint4 o = key4[i];
+            r += (o.x > m ? 1u : 0u) + (o.y > m ? 1u : 0u) + (o.z > m ? 1u : 0u) + (o.w > m ? 1u : 0u);
+        }
+        const unsigned bit = 1u << (r & 31);
+        if (atomicOr(&c.seen[r >> 5], bit) & bit) atomicOr(&c.flags, kFlagTie);
+        c.hist[j] = r;
+    }
+    g.sync();
+    const bool tie = (c.flags & kFlagTie) != 0;
+    for (unsigned j = g.lane; j < count; j += L) {
+        const unsigned long long mine = c.cand[j];
+        unsigned rank = c.hist[j];
+        if (tie) {
+            rank = 0;
+            for (unsigned i = 0; i < count; ++i) rank += c.cand[i] > mine ? 1u : 0u;
+        }
+        if (rank < k) {
+            const unsigned col = 0xFFFFu - (unsigned)(mine & 0xFFFFull);
+            const float v = row[col];
+            out_idx[rank] = (uint16_t)col;
+            out_val[rank] = v;
+            if (rank == k - 1) c.kth_bits = __float_as_uint(v) & 0x7fffffffu;
+            if (zero_selected) row[col] = 0.0f;
         }
     }
     g.sync();
@@ -200,7 +252,9 @@ __device__ __forceinline__ float group_topk_row(const RowGroup<G> &g, GroupCtl &
     constexpr int L = RowGroup<G>::L;
     const unsigned f4 = cols >> 2;
     const float4 *row4 = reinterpret_cast<const float4 *>(row);
-    if (g.lane == 0) { c.count = 0; c.nhits = 0; }
+    if (g.lane == 0) { c.count = 0; c.nhits = 0; c.flags = 0; }
+    if (g.lane < 8) c.seen[g.lane] = 0u;
+    for (unsigned i = g.lane; i < (unsigned)kCandCap / 4; i += L) reinterpret_cast<uint4 *>(c.key)[i] = make_uint4(0u, 0u, 0u, 0u);
     g.sync();
     float acc = 0.0f, first = 0.0f, second = 0.0f;
     const bool hinted = hint > 0.0f;
@@ -261,6 +315,8 @@ __device__ __forceinline__ float group_topk_row(const RowGroup<G> &g, GroupCtl &
         const unsigned mine = ge_f >= k ? fb : (ge_s >= k ? sb : 0u);
         const float bound = __uint_as_float(g.max_bits(mine, c));
         if (g.lane == 0) { c.count = 0; c.nhits = 0; }
+        // (keys of the first attempt: tops[] above overlaid only c.cand[]; stale keys beyond the new count must go)
+        for (unsigned i = g.lane; i < (unsigned)kCandCap / 4; i += L) reinterpret_cast<uint4 *>(c.key)[i] = make_uint4(0u, 0u, 0u, 0u);
         g.sync();
         if (bound > 0.0f) {
             for (unsigned i = g.lane; i < f4; i += L)
@@ -275,7 +331,7 @@ __device__ __forceinline__ float group_topk_row(const RowGroup<G> &g, GroupCtl &
             return 0.0f;
         }
     }
-    group_rank_emit<G>(g, c, row, count, k, out_idx, out_val, zero_selected);
+    group_rank_emit_keys<G>(g, c, row, count, k, out_idx, out_val, zero_selected);
     // The next row's guess: a little below this row's k-th largest, so that between k and kCandCap of its elements
     // reach it.  The window is narrow for a large k (143 of 256: a Gaussian tail has 225 elements above 0.9375 of the
     // k-th largest, too close to the cap and beyond the 256 float4 the first sweep can note), so the margin shrinks

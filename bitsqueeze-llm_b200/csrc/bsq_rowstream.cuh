@@ -26,9 +26,6 @@
 
 namespace bsq {
 
-constexpr unsigned kFlagSpecial = 1u;      // GroupCtl::flags: the row holds Inf or NaN
-constexpr unsigned kFlagSlow = 2u;         //                  some block of the row takes the literal scan
-constexpr unsigned kFlagTie = 4u;          //                  two candidates share |x|: rank on the full composite
 
 // Where a row comes from: global memory (read-only path) or a shared-memory buffer filled by a bulk copy.
 struct GlobalRow {
