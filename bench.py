@@ -586,7 +586,7 @@ def main():
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--lanes", type=int, default=4, help="matrices in flight per GPU")
+    ap.add_argument("--lanes", type=int, default=8, help="matrices in flight per GPU")
     ap.add_argument("--layers", type=int, default=None, help="batch size (default: the configuration's 32)")
     ap.add_argument("--single", default=None, choices=["C3", "C4", "C5A", "c3", "c4", "c5a"],
                     help="side measurement, not the bench line: public compress / decompress of one matrix")
@@ -644,7 +644,12 @@ def main():
     layers = shard.layers_for_rank(n_layers, rank, world)
     cnt = len(layers)
     mats = [W.config_matrix(torch, "C5A", layer=l) for l in layers]
-    lanes = max(1, min(args.lanes, max(cnt, 1)))
+    lanes = max(1, args.lanes)
+    # a rank with fewer matrices than lanes (8 ranks: 4 each) queues `mult` passes over its matrices at a time, every
+    # entry with an output buffer of its own, so that the lanes stay full; a pass is still every matrix once
+    mult = max(1, lanes // cnt) if cnt else 1
+    lanes = min(lanes, max(cnt * mult, 1))
+    entries = cnt * mult
     cfg_args = (rows, cols, cfg["outlier"], cfg["error"], cfg["rank"], cfg["niters"], cfg["uv"], cfg["s"], cfg["q"])
     batch = L.bsq_batch_create(*cfg_args, lanes)
     single = L.bsq_batch_create(*cfg_args, 1)
@@ -652,29 +657,32 @@ def main():
         raise RuntimeError("bsq_batch_create failed")
     cap = int(L.bsq_lane_packed_capacity(L.bsq_batch_lane(batch, 0)))
     VP = C.c_void_p * max(cnt, 1)
-    d_packed = [torch.empty(cap, dtype=torch.uint8, device="cuda") for _ in range(cnt)]
+    VPE = C.c_void_p * max(entries, 1)
+    d_packed = [torch.empty(cap, dtype=torch.uint8, device="cuda") for _ in range(entries)]
     d_dst = [torch.empty((rows, cols), dtype=torch.float32, device="cuda") for _ in range(lanes)]
-    in_ptrs = VP(*[m.data_ptr() for m in mats])
-    packed_ptrs = VP(*[p.data_ptr() for p in d_packed])
-    dst_ptrs = VP(*[d_dst[i % lanes].data_ptr() for i in range(cnt)])
-    hdrs = (pkg.Array * max(cnt, 1))()
-    hdr_ptrs = VP(*[C.addressof(hdrs[i]) for i in range(cnt)])
-    sizes = (C.c_uint64 * max(cnt, 1))()
+    in_ptrs = VPE(*[mats[i % cnt].data_ptr() for i in range(entries)])
+    packed_ptrs = VPE(*[p.data_ptr() for p in d_packed])
+    dst_ptrs = VPE(*[d_dst[i % lanes].data_ptr() for i in range(entries)])
+    hdrs = (pkg.Array * max(entries, 1))()
+    hdr_ptrs = VPE(*[C.addressof(hdrs[i]) for i in range(entries)])
+    sizes = (C.c_uint64 * max(entries, 1))()
     main_stream = torch.cuda.current_stream()
 
     def compress_pass(b):
-        if cnt and L.bsq_batch_compress(b, in_ptrs, cnt, pkg.INPUT_DEVICE, packed_ptrs, cap, None, hdrs, sizes) != 0:
+        """`mult` passes over this rank's matrices."""
+        if cnt and L.bsq_batch_compress(b, in_ptrs, entries, pkg.INPUT_DEVICE, packed_ptrs, cap, None, hdrs, sizes) != 0:
             raise RuntimeError("bsq_batch_compress failed")
 
     def decompress_pass(b):
-        if cnt and L.bsq_batch_decompress(b, hdr_ptrs, cnt, 1, dst_ptrs, n) != 0:
+        if cnt and L.bsq_batch_decompress(b, hdr_ptrs, entries, 1, dst_ptrs, n) != 0:
             raise RuntimeError("bsq_batch_decompress failed")
 
     def timed_steps(b, steps, passes):
-        """`steps` steps of `passes` passes each; returns (total ms, compress ms, decompress ms) from CUDA events."""
+        """`steps` steps of `passes` passes each (`passes` a multiple of `mult`); returns (total ms, compress ms, decompress ms)
+        from CUDA events."""
         evs = []
         barrier()
-        for _ in range(steps * passes):
+        for _ in range(steps * passes // mult):
             e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
             e[0].record(main_stream)
             compress_pass(b)
@@ -690,10 +698,12 @@ def main():
     for _ in range(args.warmup):
         compress_pass(batch)
         decompress_pass(batch)
-    t_est, _, _ = timed_steps(batch, 1, 1)
-    t_est = shard.max_over_ranks([t_est], device="cuda")[0]
+    t_est, _, _ = timed_steps(batch, 1, mult)
+    t_est = shard.max_over_ranks([t_est], device="cuda")[0] / mult
+    mult_all = int(shard.max_over_ranks([float(mult)], device="cuda")[0])       # the same pass count on every rank
     passes = max(1, int(math.ceil(600.0 / max(t_est * args.steps, 1e-3))))
-    err0 = rel_frob(mats[-1], d_dst[(cnt - 1) % lanes]) if cnt else None
+    passes = (passes + mult_all - 1) // mult_all * mult_all
+    err0 = rel_frob(mats[-1], d_dst[(entries - 1) % lanes]) if cnt else None
     packed_total = int(sum(sizes[i] for i in range(cnt)))
 
     sampler = ClockSampler(local_rank)
@@ -742,7 +752,7 @@ def main():
             return 0
         if L.bsq_batch_compress(batch, host_ptrs, cnt, pkg.INPUT_HOST, None, 0, outs, None, sizes) != 0:
             raise RuntimeError("bsq_batch_compress (host) failed")
-        if L.bsq_batch_decompress(batch, outs, cnt, 0, dst_ptrs, n) != 0:
+        if L.bsq_batch_decompress(batch, outs, cnt, 0, VP(*[d_dst[i % lanes].data_ptr() for i in range(cnt)]), n) != 0:
             raise RuntimeError("bsq_batch_decompress (host objects) failed")
         probe.copy_(d_dst[(cnt - 1) % lanes].view(-1)[:1])            # the step's result is read back
         got = sum(int(sizes[i]) for i in range(cnt))
@@ -819,7 +829,7 @@ def main():
             "ms_per_step": ms_total / nsteps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32 (products as 3xTF32 on tcgen05, FP32-level accuracy)", "data": "synthetic",
             "config": {"workload": WORKLOAD, "rows": rows, "cols": cols, "layers": n_layers, "passes_per_step": passes,
-                       "lanes_per_gpu": lanes,
+                       "lanes_per_gpu": lanes, "passes_queued_together": mult,
                        "parallelism": "matrix i on rank i %% %d, no collective on the data path; %d matrices in flight per GPU" % (world, lanes),
                        "l2": "every input matrix is 235 MB (> 126 MB L2)", "host_memory": "rank 0: " + numa,
                        "timed_region_s": ms_total * 1e-3},
