@@ -37,6 +37,7 @@ struct GroupCtl {
     unsigned hist[256];            // radix-select histogram of the exact path
     __align__(16) unsigned key[kCandCap];   // |x| bits of the candidates, zero beyond their number
     unsigned long long cand[kCandCap];
+    float val[kCandCap];           // the candidates' values (group_topk_row: the row itself may be gone when they are emitted)
 };
 
 template <int G>
@@ -108,6 +109,7 @@ __device__ __forceinline__ void expand_hits(const RowGroup<G> &g, GroupCtl &c, c
                 const unsigned pos = atomicAdd(&c.count, 1u);
                 if (pos < (unsigned)kCandCap) {
                     c.key[pos] = __float_as_uint(v[q]) & 0x7fffffffu;
+                    c.val[pos] = v[q];
                     c.cand[pos] = topk_composite(v[q], i * 4 + q);
                 }
             }
@@ -183,7 +185,7 @@ __device__ __forceinline__ void group_rank_emit_keys(const RowGroup<G> &g, Group
         }
         if (rank < k) {
             const unsigned col = 0xFFFFu - (unsigned)(mine & 0xFFFFull);
-            const float v = row[col];
+            const float v = c.val[j];                           // (not row[col]: without zero_selected the row may be gone)
             out_idx[rank] = (uint16_t)col;
             out_val[rank] = v;
             if (rank == k - 1) c.kth_bits = __float_as_uint(v) & 0x7fffffffu;
@@ -245,10 +247,13 @@ __device__ __noinline__ void group_topk_exact(const RowGroup<G> &g, GroupCtl &c,
 // Returns the hint for the next row; *special_out says the row holds Inf or NaN.
 // Every lane of the group calls it; the caller has synchronised the group since the row was
 // written; ends with a group sync.
-template <int G>
+// row_free(): called (by every lane, after a group sync behind the last read of the row) as soon as nothing will read
+// the row any more, if that is before the ranking -- only without zero_selected, and not on the exact path, which
+// keeps reading the row to the end; the caller may refill the buffer from then on.
+template <int G, class RowFree>
 __device__ __forceinline__ float group_topk_row(const RowGroup<G> &g, GroupCtl &c, float *row, unsigned cols, unsigned k,
                                                 uint16_t *out_idx, float *out_val, bool zero_selected, float hint,
-                                                bool *special_out) {
+                                                bool *special_out, RowFree row_free) {
     constexpr int L = RowGroup<G>::L;
     const unsigned f4 = cols >> 2;
     const float4 *row4 = reinterpret_cast<const float4 *>(row);
@@ -287,6 +292,26 @@ __device__ __forceinline__ float group_topk_row(const RowGroup<G> &g, GroupCtl &
         g.sync();
         count = c.count;
     }
+    if (hinted && (c.nhits > kHitCap || count < k || count > (unsigned)kCandCap)) {
+        // The guess was off -- by a little, most of the time (rows of one matrix differ in scale by some per cent, and
+        // for a large k the window between k and kCandCap candidates is narrow): one more sweep with the guess moved
+        // costs a tenth of working the bound out from the lanes' largest values below.
+        const float guess = hint * ((c.nhits > kHitCap || count > (unsigned)kCandCap) ? 1.0625f : 0.90625f);
+        g.sync();                                           // everybody has read nhits / count
+        if (g.lane == 0) { c.count = 0; c.nhits = 0; }
+        for (unsigned i = g.lane; i < (unsigned)kCandCap / 4; i += L) reinterpret_cast<uint4 *>(c.key)[i] = make_uint4(0u, 0u, 0u, 0u);
+        g.sync();
+#pragma unroll 4
+        for (unsigned i = g.lane; i < f4; i += L)
+            if (absmax4_nan(row4[i]) >= guess) note_hit(i, c);
+        g.sync();
+        count = 0;
+        if (c.nhits <= kHitCap) {
+            expand_hits<G>(g, c, row, guess);
+            g.sync();
+            count = c.count;
+        }
+    }
     if (!hinted || count < k || count > (unsigned)kCandCap) {
         if (k > 2u * L) {                                   // the two-per-lane bound cannot promise k entries
             group_topk_exact<G>(g, c, row, cols, k, out_idx, out_val, zero_selected);
@@ -307,10 +332,12 @@ __device__ __forceinline__ float group_topk_row(const RowGroup<G> &g, GroupCtl &
         tops[L + g.lane] = sb;
         g.sync();
         unsigned ge_f = 0, ge_s = 0;
-        for (int i = 0; i < 2 * L; ++i) {
-            const unsigned o = tops[i];
-            ge_f += o >= fb ? 1u : 0u;
-            ge_s += o >= sb ? 1u : 0u;
+        const uint4 *tops4 = reinterpret_cast<const uint4 *>(tops);
+#pragma unroll 4
+        for (int i = 0; i < 2 * L / 4; ++i) {
+            const uint4 o = tops4[i];
+            ge_f += (o.x >= fb ? 1u : 0u) + (o.y >= fb ? 1u : 0u) + (o.z >= fb ? 1u : 0u) + (o.w >= fb ? 1u : 0u);
+            ge_s += (o.x >= sb ? 1u : 0u) + (o.y >= sb ? 1u : 0u) + (o.z >= sb ? 1u : 0u) + (o.w >= sb ? 1u : 0u);
         }
         const unsigned mine = ge_f >= k ? fb : (ge_s >= k ? sb : 0u);
         const float bound = __uint_as_float(g.max_bits(mine, c));
@@ -331,6 +358,7 @@ __device__ __forceinline__ float group_topk_row(const RowGroup<G> &g, GroupCtl &
             return 0.0f;
         }
     }
+    if (!zero_selected) row_free();
     group_rank_emit_keys<G>(g, c, row, count, k, out_idx, out_val, zero_selected);
     // The next row's guess: a little below this row's k-th largest, so that between k and kCandCap of its elements
     // reach it.  The window is narrow for a large k (143 of 256: a Gaussian tail has 225 elements above 0.9375 of the

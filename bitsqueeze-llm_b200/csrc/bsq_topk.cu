@@ -43,11 +43,14 @@ __global__ void __launch_bounds__(512)
     g.sync();
     unsigned phase = 0;
     float hint = 0.0f;
-    for (unsigned r = blockIdx.x * groups_per_cta + g.gid; r < rows; r += gridDim.x * groups_per_cta) {
-        if (g.lane == 0) {
+    const unsigned row_step = gridDim.x * groups_per_cta;
+    bool next_loading = false;                               // uniform over the group: the copy of row r is already on its way
+    for (unsigned r = blockIdx.x * groups_per_cta + g.gid; r < rows; r += row_step) {
+        if (g.lane == 0 && !next_loading) {
             mbar_expect_tx(bar, bytes);
             bulk_g2s(row, in + (size_t)r * cols, bytes, bar);
         }
+        next_loading = false;
         // the outcome of the wait must be the same for every lane of the group (they meet at group barriers below):
         // a lane whose wait ran out says so, and all lanes read the same flag after a group barrier
         if (!mbar_wait_bounded(bar, phase, status)) c.wait_failed = 1;
@@ -55,8 +58,21 @@ __global__ void __launch_bounds__(512)
         if (c.wait_failed) break;
         phase ^= 1u;
         bool special = false;
+        // Extraction only (no zeroed copy wanted): once the candidates and their values are out of the row, the next
+        // row's copy starts into the same buffer while this row's candidates are still ranked and written out.
+        auto row_free = [&]() {
+            if (r + row_step < rows) {
+                fence_proxy_async_smem();
+                g.sync();
+                if (g.lane == 0) {
+                    mbar_expect_tx(bar, bytes);
+                    bulk_g2s(row, in + (size_t)(r + row_step) * cols, bytes, bar);
+                }
+                next_loading = true;
+            }
+        };
         hint = group_topk_row<G>(g, c, row, cols, k, out_idx + (size_t)r * k, out_val + (size_t)r * k, residual != nullptr,
-                                 hint, &special);
+                                 hint, &special, row_free);
         fence_proxy_async_smem();
         g.sync();
         if (residual != nullptr && g.lane == 0) {
