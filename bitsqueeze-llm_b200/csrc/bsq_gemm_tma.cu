@@ -72,6 +72,19 @@ struct Ring {
         if (++pos == n) { pos = 0; par ^= 1u; wrapped = true; }
     }
 };
+// 32-byte global accesses (sm_100): a thread of the epilogue owns a row of the tile, so every access of a warp goes to 32
+// different lines; whole 32-byte sectors halve the number of memory instructions (and of entries in the load/store
+// queue, where the epilogue warps were seen to stall) against 16-byte accesses that use half a sector each.
+__device__ __forceinline__ void ld_global_v8(const float *p, float4 &a, float4 &b) {
+    asm volatile("ld.global.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w), "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w)
+                 : "l"(p));
+}
+__device__ __forceinline__ void st_global_v8(float *p, const float4 &a, const float4 &b) {
+    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(a.x), "f"(a.y), "f"(a.z), "f"(a.w), "f"(b.x),
+                 "f"(b.y), "f"(b.z), "f"(b.w)
+                 : "memory");
+}
 __device__ __forceinline__ void tc_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -367,6 +380,9 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
         // ---- epilogue: this thread's accumulator row of every tile, 16 columns at a time ----
         const int quarter = warp & 3;                                    // the tensor-memory lanes this warp may read
         const int cb = (one_acc && warp < 7) ? 128 : 0;                  // wide tiles: first column of this warp's half of the tile
+        // 32-byte accesses need 32-byte aligned rows of C and of the minuend (tile columns start at multiples of 16)
+        const bool wide32 = ((reinterpret_cast<uintptr_t>(g.C) | (uintptr_t)(g.ldc * 4) | (uintptr_t)(g.split_stride * 4)) % 32 == 0) &&
+                            (!g.minuend || (reinterpret_cast<uintptr_t>(g.minuend) | (uintptr_t)(g.ldm * 4)) % 32 == 0);
         bool any = false;
         Ring rs(acc_sets);
         for (int i = 0; i < walk.count && ok; ++i, rs.next()) {
@@ -383,9 +399,14 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
             const bool pre = g.minuend != nullptr && ce - cb == 128 && row < g.M;
             float4 mn_pre[32];
             if (pre) {
-                const float4 *mn = reinterpret_cast<const float4 *>(g.minuend + (long)row * g.ldm + n0 + cb);
+                const float *mn = g.minuend + (long)row * g.ldm + n0 + cb;
+                if (wide32) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) mn_pre[j] = mn[j];
+                    for (int j = 0; j < 16; ++j) ld_global_v8(mn + 8 * j, mn_pre[2 * j], mn_pre[2 * j + 1]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) mn_pre[j] = reinterpret_cast<const float4 *>(mn)[j];
+                }
             }
             ok = mbar_wait_bounded(&bars.acc_full[set], rs.par, status);
             if (!ok) break;
@@ -403,6 +424,7 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
 #pragma unroll
                         for (int j = 0; j < 16; ++j) q[j] = 0x80000000u;    // (-0.0f: the sum below leaves r as it is, bit for bit)
                     }
+                    float4 o4[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const float4 m4 = mn_pre[s16 * 4 + j];
@@ -413,7 +435,14 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                         const float4 o = make_float4(__fsub_rn(m4.x, p0), __fsub_rn(m4.y, p1), __fsub_rn(m4.z, p2), __fsub_rn(m4.w, p3));
                         any |= fabsf(o.x) > 1.1920928955078125e-07f || fabsf(o.y) > 1.1920928955078125e-07f ||
                                fabsf(o.z) > 1.1920928955078125e-07f || fabsf(o.w) > 1.1920928955078125e-07f;
-                        dst[s16 * 4 + j] = o;
+                        o4[j] = o;
+                    }
+                    if (wide32) {
+                        st_global_v8(reinterpret_cast<float *>(dst + s16 * 4), o4[0], o4[1]);
+                        st_global_v8(reinterpret_cast<float *>(dst + s16 * 4 + 2), o4[2], o4[3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) dst[s16 * 4 + j] = o4[j];
                     }
                 }
             } else
@@ -440,6 +469,11 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                                    fabsf(o.z) > 1.1920928955078125e-07f || fabsf(o.w) > 1.1920928955078125e-07f;
                             dst[j] = o;
                         }
+                    } else if (wide32) {
+                        st_global_v8(reinterpret_cast<float *>(dst), make_float4(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]), __uint_as_float(r[3])),
+                                     make_float4(__uint_as_float(r[4]), __uint_as_float(r[5]), __uint_as_float(r[6]), __uint_as_float(r[7])));
+                        st_global_v8(reinterpret_cast<float *>(dst + 2), make_float4(__uint_as_float(r[8]), __uint_as_float(r[9]), __uint_as_float(r[10]), __uint_as_float(r[11])),
+                                     make_float4(__uint_as_float(r[12]), __uint_as_float(r[13]), __uint_as_float(r[14]), __uint_as_float(r[15])));
                     } else {
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
