@@ -162,6 +162,8 @@ __device__ __forceinline__ void tile_epilogue(const GemmArgs &g, unsigned tmem_d
     const int half = (N / 16 + 1) / 2 * 16;                  // columns of the lower half, a multiple of 16
     const int c_begin = warp < 4 ? 0 : half, c_end = warp < 4 ? half : N;
     bool any = false;
+    // 32-byte stores need 32-byte aligned rows of C (tile columns start at multiples of 16)
+    const bool wide32 = (reinterpret_cast<uintptr_t>(g.C) | (uintptr_t)(g.ldc * 4) | (uintptr_t)(g.split_stride * 4)) % 32 == 0;
     if (ok) {
         for (int c0 = c_begin; c0 < c_end; c0 += 16) {
             unsigned r[16], q[16];
@@ -189,6 +191,11 @@ __device__ __forceinline__ void tile_epilogue(const GemmArgs &g, unsigned tmem_d
                                fabsf(o.z) > 1.1920928955078125e-07f || fabsf(o.w) > 1.1920928955078125e-07f;
                         dst[j] = o;
                     }
+                } else if (wide32) {
+                    st_global_v8(reinterpret_cast<float *>(dst), make_float4(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]), __uint_as_float(r[3])),
+                                 make_float4(__uint_as_float(r[4]), __uint_as_float(r[5]), __uint_as_float(r[6]), __uint_as_float(r[7])));
+                    st_global_v8(reinterpret_cast<float *>(dst + 2), make_float4(__uint_as_float(r[8]), __uint_as_float(r[9]), __uint_as_float(r[10]), __uint_as_float(r[11])),
+                                 make_float4(__uint_as_float(r[12]), __uint_as_float(r[13]), __uint_as_float(r[14]), __uint_as_float(r[15])));
                 } else {
 #pragma unroll
                     for (int j = 0; j < 4; ++j)

@@ -72,19 +72,6 @@ struct Ring {
         if (++pos == n) { pos = 0; par ^= 1u; wrapped = true; }
     }
 };
-// 32-byte global accesses (sm_100): a thread of the epilogue owns a row of the tile, so every access of a warp goes to 32
-// different lines; whole 32-byte sectors halve the number of memory instructions (and of entries in the load/store
-// queue, where the epilogue warps were seen to stall) against 16-byte accesses that use half a sector each.
-__device__ __forceinline__ void ld_global_v8(const float *p, float4 &a, float4 &b) {
-    asm volatile("ld.global.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w), "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w)
-                 : "l"(p));
-}
-__device__ __forceinline__ void st_global_v8(float *p, const float4 &a, const float4 &b) {
-    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(a.x), "f"(a.y), "f"(a.z), "f"(a.w), "f"(b.x),
-                 "f"(b.y), "f"(b.z), "f"(b.w)
-                 : "memory");
-}
 __device__ __forceinline__ void tc_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
