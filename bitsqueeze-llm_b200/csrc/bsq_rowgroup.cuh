@@ -292,11 +292,18 @@ __device__ __forceinline__ float group_topk_row(const RowGroup<G> &g, GroupCtl &
         g.sync();
         count = c.count;
     }
-    if (hinted && (c.nhits > kHitCap || count < k || count > (unsigned)kCandCap)) {
+    float guess = hint;
+    for (int retry = 0; retry < 2 && hinted && (c.nhits > kHitCap || count < k || count > (unsigned)kCandCap); ++retry) {
         // The guess was off -- by a little, most of the time (rows of one matrix differ in scale by some per cent, and
-        // for a large k the window between k and kCandCap candidates is narrow): one more sweep with the guess moved
-        // costs a tenth of working the bound out from the lanes' largest values below.
-        const float guess = hint * ((c.nhits > kHitCap || count > (unsigned)kCandCap) ? 1.0625f : 0.90625f);
+        // for a large k the window between k and kCandCap candidates is narrow): another sweep with the guess moved
+        // costs a tenth of working the bound out from the lanes' largest values below.  How far to move it: the number
+        // that got through (the float4 hits when they overflowed: a lower bound) against a target inside the window
+        // (its middle, or 1.6 k where that is less: ranking costs count^2),
+        // with the slope of a Gaussian tail near its 1 % quantile, d ln(count) / d ln(bound) = -z^2 ~ -6.6.
+        const float passed = (float)max(c.nhits > kHitCap ? c.nhits : count, 1u);
+        const float target = fminf(0.5f * (float)(k + (unsigned)kCandCap), 1.6f * (float)k);
+        const float factor = exp2f(0.15f * log2f(passed / target));
+        guess *= fminf(fmaxf(factor, 0.7f), 1.4f);
         g.sync();                                           // everybody has read nhits / count
         if (g.lane == 0) { c.count = 0; c.nhits = 0; }
         for (unsigned i = g.lane; i < (unsigned)kCandCap / 4; i += L) reinterpret_cast<uint4 *>(c.key)[i] = make_uint4(0u, 0u, 0u, 0u);
