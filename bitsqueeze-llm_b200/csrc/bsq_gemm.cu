@@ -221,6 +221,16 @@ bool wide_tiles_enabled() {
     return on;
 }
 
+// BSQ_GEMM_F16: 0 TF32 halves everywhere; 1 (default): FP16 halves where the caller gives a bound on |A|; 2: also where it
+// does not (a pass over A per product).
+int f16_mode() {
+    static const int mode = [] {
+        const char *e = std::getenv("BSQ_GEMM_F16");
+        return e && e[0] >= '0' && e[0] <= '2' ? e[0] - '0' : 1;
+    }();
+    return mode;
+}
+
 // BSQ_GEMM_TC=0 keeps every product on the FP32 pipes (for A/B comparisons of the two kernels).
 bool tensor_cores_enabled() {
     static const bool on = [] {
@@ -237,15 +247,15 @@ size_t gemm_workspace_bytes(int M, int N, int max_splits) { return (size_t)M * N
 // Picks the K split so that about two CTAs per SM are busy; partials go to `workspace` (may be null: no split).
 cudaError_t gemm(bool a_kmajor, bool b_kmajor, const float *A, long lda, const float *B, long ldb, float *C, long ldc, int M,
                  int N, int K, const float *kscale, const float *minuend, long ldm, unsigned *flag, unsigned *status,
-                 float *workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream) {
+                 float *workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream, const unsigned *a_absmax_bits) {
     return gemm_select(tensor_cores_enabled(), a_kmajor, b_kmajor, A, lda, B, ldb, C, ldc, M, N, K, kscale, minuend, ldm, flag,
-                       status, workspace, workspace_bytes, sm_count, stream);
+                       status, workspace, workspace_bytes, sm_count, stream, a_absmax_bits);
 }
 
 cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, const float *A, long lda, const float *B, long ldb,
                         float *C, long ldc, int M, int N, int K, const float *kscale, const float *minuend, long ldm,
                         unsigned *flag, unsigned *status, float *workspace, size_t workspace_bytes, int sm_count,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, const unsigned *a_absmax_bits) {
     if (M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
     if (allow_tensor_cores) {
         // tensor-core path: one 128-row tile per CTA, two CTAs per SM up to N = 128; K is split so that the tiles fill
@@ -303,7 +313,23 @@ cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, c
             }
         }
         const int slots = (t.use_tma ? 1 : with_image ? gemm_tc_image_ctas_per_sm(t.n_tile) : (t.n_tile <= 128 ? 2 : 1)) * sm_count;
-        if (t.use_tma) gemm_tc_tma_rings(t.n_tile, a_kmajor, &t.raw_stages, &t.a_stages, &t.b_stages);
+        // the FP16 form of the split (BSQ_GEMM_F16=1; =2 also without a given bound on |A|: it is then worked out here,
+        // a pass over A): 256-column products with A contiguous along K on the TMA-fed kernel
+        if (t.use_tma && !t.persistent && t.n_tile == 256 && !kscale && !minuend && workspace_bytes >= 4096 &&
+            (f16_mode() == 2 || (f16_mode() == 1 && a_absmax_bits))) {
+            unsigned *words = reinterpret_cast<unsigned *>(workspace);      // [0]: |B| max, [1]: |A| max when not given
+            workspace += 64;
+            workspace_bytes -= 256;
+            t.f16 = true;
+            t.b_absmax_bits = words;
+            t.a_absmax_bits = a_absmax_bits;
+            if (!a_absmax_bits) {
+                const cudaError_t e = gemm_absmax_bits(A, lda, a_kmajor ? M : K, a_kmajor ? K : M, words + 1, stream);
+                if (e != cudaSuccess) return e;
+                t.a_absmax_bits = words + 1;
+            }
+        }
+        if (t.use_tma) gemm_tc_tma_rings(t.n_tile, a_kmajor, &t.raw_stages, &t.a_stages, &t.b_stages, t.f16);
         else if (with_image) gemm_tc_image_rings(t.n_tile, &t.a_stages, &t.b_stages);
         if (workspace && !minuend && !kscale && tiles_tc < slots) {
             const int max_by_k = max(1, K / 256);             // a split below 256 of K costs more in the reduction than it gains
@@ -312,7 +338,7 @@ cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, c
         }
         if (with_image) t.b_image = reinterpret_cast<const float4 *>(reinterpret_cast<unsigned char *>(workspace) + workspace_bytes);
         t.splits = splits_tc;
-        t.k_per_split = ((K + splits_tc - 1) / splits_tc + 31) / 32 * 32;
+        t.k_per_split = t.f16 ? ((K + splits_tc - 1) / splits_tc + 63) / 64 * 64 : ((K + splits_tc - 1) / splits_tc + 31) / 32 * 32;
         t.splits = (K + t.k_per_split - 1) / t.k_per_split;                    // no empty split
         if (t.splits > 1) {
             t.C = workspace; t.ldc = N; t.split_stride = (long)M * N;

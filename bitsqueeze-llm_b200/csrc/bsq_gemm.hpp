@@ -34,6 +34,9 @@ struct GemmArgs {
                                // column of C half as many barrier waits, descriptors and commits for the one thread that issues
                                // the MMAs, which is what bounds a product with a short K
     int sm_count;
+    bool f16;                      // TMA-fed kernel: operands split into two FP16 halves (bsq_gemm_tc.cuh) instead of two TF32
+    const unsigned *a_absmax_bits; // halves; device words with the bits of the largest |A| and |B| (finite), from which the
+    const unsigned *b_absmax_bits; // power-of-two scales of the split come
 };
 
 // Tensor-core path: true if the shape qualifies (N a multiple of 16, 16-byte aligned operands with leading
@@ -44,6 +47,8 @@ bool gemm_tc_eligible(const GemmArgs &g, bool a_kmajor, bool b_kmajor);
 // fetches them by bulk copies; gemm_tc_image_bytes is the room that takes.
 size_t gemm_tc_image_bytes(int N, int n_tile, int K);
 size_t gemm_tc_a_image_bytes(int M, int K);
+// bits of the largest |x| of a rows x cols matrix into *d_out (the scale of the FP16 split comes from it)
+cudaError_t gemm_absmax_bits(const float *x, long ld, int rows, int cols, unsigned *d_out, cudaStream_t stream);
 int gemm_tc_image_ctas_per_sm(int n_tile);
 void gemm_tc_image_rings(int n_tile, int *sa, int *nb);
 cudaError_t gemm_tc_launch(const GemmArgs &g, bool a_kmajor, bool b_kmajor, unsigned *status, cudaStream_t stream);
@@ -53,7 +58,7 @@ cudaError_t gemm_tc_launch(const GemmArgs &g, bool a_kmajor, bool b_kmajor, unsi
 // BSQ_GEMM_TMA switch; gemm_tc_tma_rings gives the ring lengths for raw_stages / a_stages / b_stages.
 bool gemm_tc_tma_enabled();
 bool gemm_tc_tma_usable(const GemmArgs &g, bool a_kmajor);
-void gemm_tc_tma_rings(int n_tile, bool a_kmajor, int *nraw, int *nr, int *nb);
+void gemm_tc_tma_rings(int n_tile, bool a_kmajor, int *nraw, int *nr, int *nb, bool f16 = false);
 cudaError_t gemm_tc_tma_launch(const GemmArgs &g, bool a_kmajor, unsigned *status, cudaStream_t stream);
 
 }  // namespace bsq

@@ -509,6 +509,62 @@ __global__ void __launch_bounds__(256) presplit_a_kernel(const float *__restrict
     split_store(v, hi, hi + (long)rows_pad * k4);
 }
 
+// The largest |x| of a rows x cols matrix (leading dimension ld) as float bits, by atomicMax into *out (cleared by the
+// caller).  Non-finite values leave bits >= 0x7f800000 there, which split16_scale answers with... a scale that no
+// longer matters: the product is NaN or Inf then, as it is for the reference.
+__global__ void __launch_bounds__(256) absmax_bits_kernel(const float *__restrict__ x, long ld, int rows, int cols, unsigned *out) {
+    const int c4 = cols / 4;
+    unsigned m = 0;
+    for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < (long)rows * c4; e += (long)gridDim.x * blockDim.x) {
+        const float4 v = *reinterpret_cast<const float4 *>(x + (e / c4) * ld + (e % c4) * 4);
+        m = max(max(m, __float_as_uint(v.x) & 0x7fffffffu), max(__float_as_uint(v.y) & 0x7fffffffu, max(__float_as_uint(v.z) & 0x7fffffffu, __float_as_uint(v.w) & 0x7fffffffu)));
+    }
+    m = __reduce_max_sync(0xffffffffu, m);
+    if ((threadIdx.x & 31) == 0 && m) atomicMax(out, m);
+}
+
+// The FP16 form of presplit_b_kernel: one thread per (chunk of 32 k, unit of 8 k, column): the eight values
+// B(32 c + 8 kc .. + 7, n0 + r), scaled, as the hi and the lo unit of the chunk's image (same unit order and image size
+// as the TF32 images, which hold 16 k per chunk).  k past K gives zeros.
+template <bool B_KMAJOR>
+__global__ void __launch_bounds__(256) presplit_b16_kernel(const float *__restrict__ B, long ldb, int N, int K, int n_tile, int chunks,
+                                                           uint4 *__restrict__ image, const unsigned *__restrict__ absmax_bits) {
+    const int n0 = blockIdx.y * n_tile;
+    const int Nt = min(n_tile, N - n0);
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)chunks * 4 * Nt) return;
+    int kc, r;
+    if (B_KMAJOR) {
+        kc = (int)(idx % 4);
+        r = (int)((idx / 4) % Nt);
+    } else {
+        r = (int)(idx % Nt);
+        kc = (int)((idx / Nt) % 4);
+    }
+    const long c = idx / (4 * Nt);
+    const long k = c * 32 + kc * 8;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (B_KMAJOR) {
+        const float *p = B + (long)(n0 + r) * ldb + k;
+        if (k + 7 < K) {
+            const float4 q0 = *reinterpret_cast<const float4 *>(p), q1 = *reinterpret_cast<const float4 *>(p + 4);
+            v[0] = q0.x; v[1] = q0.y; v[2] = q0.z; v[3] = q0.w; v[4] = q1.x; v[5] = q1.y; v[6] = q1.z; v[7] = q1.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (k + j < K) v[j] = p[j];
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (k + j < K) v[j] = B[(k + j) * ldb + n0 + r];
+    }
+    uint4 *img = image + ((size_t)blockIdx.y * chunks + c) * image_units(n_tile);
+    const unsigned u = image_unit_index(kc, r, Nt);
+    split16_store8(make_float4(v[0], v[1], v[2], v[3]), make_float4(v[4], v[5], v[6], v[7]), split16_scale(*absmax_bits), img + u,
+                   img + image_half_units(Nt) + u);
+}
+
 template <bool A_KMAJOR, int NMAX>
 __global__ void __launch_bounds__(NT2, NMAX <= 128 ? 2 : 1) gemm_tc_image_kernel(GemmArgs g, unsigned *status) {
     // chunks of A in flight in registers per thread: what is in flight per SM is what bounds these products (the
@@ -688,12 +744,22 @@ size_t tc_image_smem_bytes(int N, int sa, int nb) { return ((size_t)sa * 2 * sta
 
 template <bool AK, int NMAX>
 cudaError_t launch_image(const GemmArgs &g, bool b_kmajor, unsigned *status, cudaStream_t stream) {
-    const int chunks = (g.K + TK - 1) / TK, n_tiles = (g.N + g.n_tile - 1) / g.n_tile;
+    const int chunks = g.f16 ? (g.K + 31) / 32 : (g.K + TK - 1) / TK, n_tiles = (g.N + g.n_tile - 1) / g.n_tile;
     float4 *image = const_cast<float4 *>(g.b_image);
     dim3 pgrid((unsigned)(((long)chunks * 4 * g.n_tile + 255) / 256), n_tiles, 1);
-    if (b_kmajor) presplit_b_kernel<true><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image);
+    cudaError_t err;
+    if (g.f16) {
+        // the scale of B's split comes from its largest magnitude (B is a panel: a pass over it costs microseconds)
+        unsigned *bmax = const_cast<unsigned *>(g.b_absmax_bits);
+        if ((err = cudaMemsetAsync(bmax, 0, sizeof(unsigned), stream)) != cudaSuccess) return err;
+        const int b_rows = b_kmajor ? g.N : g.K, b_cols = b_kmajor ? g.K : g.N;
+        absmax_bits_kernel<<<296, 256, 0, stream>>>(g.B, g.ldb, b_rows, b_cols, bmax);
+        uint4 *image16 = reinterpret_cast<uint4 *>(image);
+        if (b_kmajor) presplit_b16_kernel<true><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image16, bmax);
+        else presplit_b16_kernel<false><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image16, bmax);
+    } else if (b_kmajor) presplit_b_kernel<true><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image);
     else presplit_b_kernel<false><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image);
-    cudaError_t err = cudaGetLastError();
+    err = cudaGetLastError();
     if (err != cudaSuccess) return err;
     if (g.use_tma && g.a_image) {
         const long quads = (long)g.a_image_rows * (g.K / 4);
@@ -720,6 +786,14 @@ int gemm_tc_image_ctas_per_sm(int n_tile) {
     return by_smem < by_tmem ? (by_smem < 1 ? 1 : by_smem) : by_tmem;
 }
 void gemm_tc_image_rings(int n_tile, int *sa, int *nb) { tc_image_rings(n_tile, sa, nb); }
+
+cudaError_t gemm_absmax_bits(const float *x, long ld, int rows, int cols, unsigned *d_out, cudaStream_t stream) {
+    if (cols % 4 != 0 || ld % 4 != 0 || reinterpret_cast<uintptr_t>(x) % 16 != 0) return cudaErrorInvalidValue;
+    cudaError_t err = cudaMemsetAsync(d_out, 0, sizeof(unsigned), stream);
+    if (err != cudaSuccess) return err;
+    absmax_bits_kernel<<<592, 256, 0, stream>>>(x, ld, rows, cols, d_out);
+    return cudaGetLastError();
+}
 
 size_t gemm_tc_a_image_bytes(int M, int K) { return (size_t)2 * ((M + TM - 1) / TM * TM) * K * sizeof(float); }
 

@@ -3,6 +3,8 @@
 // into beforehand.
 #pragma once
 
+#include <cuda_fp16.h>
+
 #include "bsq_device.cuh"
 #include "bsq_gemm.hpp"
 
@@ -28,6 +30,18 @@ __device__ __forceinline__ void mma_tf32(unsigned tmem_d, uint64_t desc_a, uint6
         ".reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+
+__device__ __forceinline__ void mma_f16(unsigned tmem_d, uint64_t desc_a, uint64_t desc_b, unsigned idesc, bool accumulate) {
+    const unsigned acc = accumulate ? 1u : 0u;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t"
         "}\n" ::"r"(tmem_d),
         "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
         : "memory");
@@ -68,6 +82,36 @@ __device__ __forceinline__ void split_store(float4 v, float4 *hi, float4 *lo) {
     *hi = h;
     *lo = make_float4(tf32_rna(__fsub_rn(v.x, h.x)), tf32_rna(__fsub_rn(v.y, h.y)), tf32_rna(__fsub_rn(v.z, h.z)),
                       tf32_rna(__fsub_rn(v.w, h.w)));
+}
+
+// The FP16 form of the split: x * s = hi + lo' / 2^11 (+ e, |e| <= 2^-22 |x * s|) with hi = fp16(x * s) and
+// lo' = fp16((x * s - hi) * 2^11), s a power of two that brings the operand's largest magnitude into [2^14, 2^15):
+// hi carries 11 significant bits and lo' the next 11, like the two TF32 halves, and lo' has hi's magnitude, so both sit
+// in FP16's range (elements below 2^-28 of the largest lose bits, an absolute error below FP32's on the largest).
+// hi * hi goes into one accumulator, lo' * hi + hi * lo' into the other, which the epilogue scales by 2^-11.
+constexpr float kSplit16LoScale = 2048.0f;
+__device__ __forceinline__ float split16_scale(unsigned absmax_bits) {           // from the bits of the largest |x| (finite)
+    const int e = (int)((absmax_bits >> 23) & 0xFFu) - 127;
+    return absmax_bits == 0u ? 1.0f : exp2f((float)(14 - e));
+}
+// eight consecutive k of one row: two 16-byte units (hi, lo).  hi is taken as a float first, by the integer rounding
+// of tf32_rna (FP16 has TF32's 10 mantissa bits, so the value converts exactly wherever FP16 is normal), which leaves
+// one conversion instruction per pair of halves (cvt.rn.f16x2.f32) instead of three conversions per element.
+__device__ __forceinline__ void split16_store8(const float4 &a, const float4 &b, float s, uint4 *hi, uint4 *lo) {
+    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float h[8], l[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float xs = v[i] * s;
+        h[i] = tf32_rna(xs);
+        l[i] = (xs - h[i]) * kSplit16LoScale;
+    }
+    auto pack = [](float p, float q) {
+        const __half2 r = __floats2half2_rn(p, q);
+        return *reinterpret_cast<const unsigned *>(&r);
+    };
+    *hi = make_uint4(pack(h[0], h[1]), pack(h[2], h[3]), pack(h[4], h[5]), pack(h[6], h[7]));
+    *lo = make_uint4(pack(l[0], l[1]), pack(l[2], l[3]), pack(l[4], l[5]), pack(l[6], l[7]));
 }
 
 // A B image is dense (nobody stores into it with a pattern that could conflict): core matrices of 8 columns x 16 B

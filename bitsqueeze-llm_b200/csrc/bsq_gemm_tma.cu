@@ -123,11 +123,19 @@ struct TileWalk {
 // thread m gathers the four k of a unit from four rows of the box (a warp reads 32 neighbouring floats of one k: no
 // bank conflict, the swizzle only permutes 16-byte pieces) and writes hi and lo into row m of an operand stage in the
 // same K-major swizzled layout as above.  The raw box is handed back to the producer as soon as it has been read.
-template <bool A_KMAJOR, int NMAX>
+// F16 = true: the operands are split into two FP16 halves instead of two TF32 halves (see split16 in bsq_gemm_tc.cuh):
+// all layouts keep their BYTES (a 128-byte operand row now holds 64 of K, an image of B 32 of K), so descriptors, rings
+// and the MMA issue loop are the same; the caller's FP32 boxes go through the raw ring in both orientations, because
+// the 16-bit images cannot be made in place.
+template <bool A_KMAJOR, int NMAX, bool F16 = false>
 __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_constant__ CUtensorMap tmap_a, GemmArgs g, unsigned *status) {
     extern __shared__ unsigned char smem_dyn[];
     unsigned char *base = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);      // the swizzle wants 1024-byte aligned slots
-    const int NR = g.a_stages, NB = g.b_stages, NRAW = A_KMAJOR ? 0 : g.raw_stages;
+    constexpr int KS = F16 ? 64 : bsq::KS;                 // K per slot of A
+    constexpr int TK = F16 ? 32 : bsq::TK;                 // K per image of B
+    constexpr bool USES_RAW = !A_KMAJOR || F16;
+    constexpr unsigned RAW_SLOT = F16 ? 2u * bsq::RAW_SLOT : bsq::RAW_SLOT;
+    const int NR = g.a_stages, NB = g.b_stages, NRAW = USES_RAW ? g.raw_stages : 0;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool a_img = A_KMAJOR && g.a_image != nullptr;           // A split beforehand: both halves of a slot come in by TMA
     const unsigned b_stride = 2u * image_half_units(g.n_tile) * 16u;
@@ -181,7 +189,7 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
         // ---- A producer: one box per slot, as far ahead as the ring allows ----
         if (lane == 0) {
             int ca = 0;                                                  // slots filled so far, over all tiles
-            Ring ra(A_KMAJOR ? NR : NRAW);
+            Ring ra(USES_RAW ? NRAW : NR);
             for (int i = 0; i < walk.count && ok; ++i) {
                 int mt, nt, z;
                 walk.at(i, &mt, &nt, &z);
@@ -189,7 +197,15 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                 const int chunks_a = (k_end - k_begin + KS - 1) / KS;
                 for (int c = 0; c < chunks_a; ++c, ++ca, ra.next()) {
                     const int s = ra.pos;
-                    if (A_KMAJOR) {
+                    if (A_KMAJOR && F16) {
+                        // two boxes of 32 k x 128 rows, as they are in the caller's matrix; the transform warps make the
+                        // slot's two FP16 images from them
+                        if (ra.wrapped) ok = mbar_wait_bounded(&bars.raw_empty[s], ra.par ^ 1u, status);
+                        if (!ok) break;
+                        mbar_expect_tx(&bars.raw_full[s], RAW_SLOT);
+                        tma_load_2d(raw_slots + (size_t)s * RAW_SLOT, &tmap_a, k_begin + c * KS, mt * TM, &bars.raw_full[s]);
+                        tma_load_2d(raw_slots + (size_t)s * RAW_SLOT + RAW_SLOT / 2, &tmap_a, k_begin + c * KS + 32, mt * TM, &bars.raw_full[s]);
+                    } else if (A_KMAJOR) {
                         if (ra.wrapped) ok = mbar_wait_bounded(&bars.empty_a[s], ra.par ^ 1u, status);
                         if (!ok) break;
                         if (a_img) {                                     // hi and lo of the slot, split beforehand
@@ -205,15 +221,18 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                         if (!ok) break;
                         mbar_expect_tx(&bars.raw_full[s], RAW_SLOT);
 #pragma unroll
-                        for (int b = 0; b < 4; ++b)           // inner coordinate: the row (contiguous), outer: k
-                            tma_load_2d(raw_slots + (size_t)s * RAW_SLOT + b * RAW_BOX, &tmap_a, mt * TM + 32 * b, k_begin + c * KS, &bars.raw_full[s]);
+                        for (int kg = 0; kg < (F16 ? 2 : 1); ++kg)       // (F16: a slot is 64 of k, two boxes deep)
+#pragma unroll
+                            for (int b = 0; b < 4; ++b)       // inner coordinate: the row (contiguous), outer: k
+                                tma_load_2d(raw_slots + (size_t)s * RAW_SLOT + (kg * 4 + b) * RAW_BOX, &tmap_a, mt * TM + 32 * b,
+                                            k_begin + c * KS + 32 * kg, &bars.raw_full[s]);
                     }
                 }
             }
             if (!ok) {
                 // leaving early: boxes still in flight must have landed before this CTA's shared memory goes away
                 atomicOr(&bars.failed, 1u);
-                if (A_KMAJOR)
+                if (!USES_RAW)
                     for (int c = max(0, ca - NR); c < ca; ++c) mbar_wait_bounded(&bars.full_a[c % NR], (unsigned)(c / NR) & 1u, status);
                 else
                     for (int c = max(0, ca - NRAW); c < ca; ++c) mbar_wait_bounded(&bars.raw_full[c % NRAW], (unsigned)(c / NRAW) & 1u, status);
@@ -257,7 +276,8 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                 const int N = min(g.n_tile, g.N - nt * g.n_tile);
                 const unsigned b_units = image_half_units(N);
                 // FP32 accumulate, TF32 x TF32, both operands K-major, N >> 3, M >> 4
-                const unsigned idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned)(N >> 3) << 17) | ((unsigned)(TM >> 4) << 24);
+                // (F16: A and B formats 0 = FP16 instead of 2 = TF32, and the instruction is kind::f16, 16 of K each)
+                const unsigned idesc = (1u << 4) | ((F16 ? 0u : 2u) << 7) | ((F16 ? 0u : 2u) << 10) | ((unsigned)(N >> 3) << 17) | ((unsigned)(TM >> 4) << 24);
                 const unsigned b_kstep = 2u * (unsigned)N;              // units from one 8-wide k-step of an image to the next
                 const int set = rs.pos;
                 const unsigned acc = tmem_d + (unsigned)set * acc_stride, acc_x = one_acc ? acc : acc + acc_cols;
@@ -280,13 +300,19 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint64_t db0 = smem_desc(smem_u32(b_slots + (size_t)sb * b_stride), (unsigned)N * 16u, 128u);
 #pragma unroll
-                        for (int ks = 0; ks < TK / 8; ++ks) {
+                        for (int ks = 0; ks < 2; ++ks) {                 // two k-steps of 32 bytes of K per image
                             const int kk = 2 * h + ks;                   // k-step of 8 inside the slot's 32
                             const uint64_t dah = da_hi + (uint64_t)(kk * 2), dal = da_lo + (uint64_t)(kk * 2);
                             const uint64_t dbh = db0 + (uint64_t)(ks * b_kstep), dbl = dbh + b_units;
-                            mma_tf32(acc, dah, dbh, idesc, c > 0 || kk > 0);
-                            mma_tf32(acc_x, dal, dbh, idesc, one_acc || c > 0 || kk > 0);
-                            mma_tf32(acc_x, dah, dbl, idesc, true);
+                            if (F16) {
+                                mma_f16(acc, dah, dbh, idesc, c > 0 || kk > 0);
+                                mma_f16(acc_x, dal, dbh, idesc, one_acc || c > 0 || kk > 0);
+                                mma_f16(acc_x, dah, dbl, idesc, true);
+                            } else {
+                                mma_tf32(acc, dah, dbh, idesc, c > 0 || kk > 0);
+                                mma_tf32(acc_x, dal, dbh, idesc, one_acc || c > 0 || kk > 0);
+                                mma_tf32(acc_x, dah, dbl, idesc, true);
+                            }
                         }
                         tc_commit(&bars.empty_b[sb]);
                         rb.next();
@@ -300,7 +326,8 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
     } else if (warp < 7 && !one_acc) {
         // ---- transform: hi in place, lo behind it (nothing to do when A was split beforehand) ----
         const int t = tid - 3 * 32;
-        Ring ra(NR), rr(A_KMAJOR ? 1 : NRAW);
+        Ring ra(NR), rr(USES_RAW ? NRAW : 1);
+        const float sa16 = F16 ? split16_scale(*g.a_absmax_bits) : 1.0f;
         for (int i = 0; i < (a_img ? 0 : walk.count) && ok; ++i) {
             int mt, nt, z;
             walk.at(i, &mt, &nt, &z);
@@ -310,12 +337,66 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                 const int s = ra.pos;
                 float4 *hi = reinterpret_cast<float4 *>(a_slots + (size_t)s * A_SLOT);
                 float4 *lo = hi + A_HALF / 16;
+                if (A_KMAJOR && F16) {
+                    const int sr = rr.pos;
+                    ok = mbar_wait_bounded(&bars.raw_full[sr], rr.par, status);
+                    if (ok && ra.wrapped) ok = mbar_wait_bounded(&bars.empty_a[s], ra.par ^ 1u, status);
+                    if (!ok) break;
+                    // thread t owns row t: its 64 k are 8 units of 4 k in each of the slot's two boxes (unit u of row t
+                    // sits at position u ^ (t & 7)); they become 8 units of 8 FP16 k in the hi and in the lo image
+                    const float4 *box0 = reinterpret_cast<const float4 *>(raw_slots + (size_t)sr * RAW_SLOT), *box1 = box0 + RAW_SLOT / 32;
+                    float4 w[16];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        w[u] = box0[t * 8 + (u ^ (t & 7))];
+                        w[8 + u] = box1[t * 8 + (u ^ (t & 7))];
+                    }
+                    mbar_arrive(&bars.raw_empty[sr]);
+                    uint4 *hi16 = reinterpret_cast<uint4 *>(hi), *lo16 = reinterpret_cast<uint4 *>(lo);
+#pragma unroll
+                    for (int c8 = 0; c8 < 8; ++c8) {
+                        const int at = t * 8 + (c8 ^ (t & 7));
+                        split16_store8(w[2 * c8], w[2 * c8 + 1], sa16, hi16 + at, lo16 + at);
+                    }
+                    fence_proxy_async_smem();
+                    mbar_arrive(&bars.ready_a[s]);
+                    continue;
+                }
                 if (!A_KMAJOR) {
                     const int sr = rr.pos;
                     ok = mbar_wait_bounded(&bars.raw_full[sr], rr.par, status);
                     // the MMAs that read this operand stage NR slots ago must be done with it
                     if (ok && ra.wrapped) ok = mbar_wait_bounded(&bars.empty_a[s], ra.par ^ 1u, status);
                     if (!ok) break;
+                    if (F16) {
+                        // thread t owns row t of the slot: float t % 32 of every k in boxes t / 32 (k 0..31) and 4 + t / 32
+                        float4 w[16];
+#pragma unroll
+                        for (int kg = 0; kg < 2; ++kg) {
+                            const float *bx = reinterpret_cast<const float *>(raw_slots + (size_t)sr * RAW_SLOT + (kg * 4 + (t >> 5)) * RAW_BOX);
+                            const int mm = t & 31;
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                float e[4];
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) {
+                                    const int kk = 4 * q + u;
+                                    e[u] = bx[kk * 32 + ((((mm >> 2) ^ (kk & 7)) << 2) | (mm & 3))];
+                                }
+                                w[kg * 8 + q] = make_float4(e[0], e[1], e[2], e[3]);
+                            }
+                        }
+                        mbar_arrive(&bars.raw_empty[sr]);
+                        uint4 *hi16 = reinterpret_cast<uint4 *>(hi), *lo16 = reinterpret_cast<uint4 *>(lo);
+#pragma unroll
+                        for (int c8 = 0; c8 < 8; ++c8) {
+                            const int at = t * 8 + (c8 ^ (t & 7));
+                            split16_store8(w[2 * c8], w[2 * c8 + 1], sa16, hi16 + at, lo16 + at);
+                        }
+                        fence_proxy_async_smem();
+                        mbar_arrive(&bars.ready_a[s]);
+                        continue;
+                    }
                     // thread t owns row t of the slot: box t / 32, float t % 32 of every k
                     const float *box = reinterpret_cast<const float *>(raw_slots + (size_t)sr * RAW_SLOT + (t >> 5) * RAW_BOX);
                     const int mm = t & 31, k0 = k_begin + c * KS;
@@ -367,6 +448,7 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
         // ---- epilogue: this thread's accumulator row of every tile, 16 columns at a time ----
         const int quarter = warp & 3;                                    // the tensor-memory lanes this warp may read
         const int cb = (one_acc && warp < 7) ? 128 : 0;                  // wide tiles: first column of this warp's half of the tile
+        const float inv16 = F16 ? 1.0f / (split16_scale(*g.a_absmax_bits) * split16_scale(*g.b_absmax_bits)) : 1.0f;
         // 32-byte accesses need 32-byte aligned rows of C and of the minuend (tile columns start at multiples of 16)
         const bool wide32 = ((reinterpret_cast<uintptr_t>(g.C) | (uintptr_t)(g.ldc * 4) | (uintptr_t)(g.split_stride * 4)) % 32 == 0) &&
                             (!g.minuend || (reinterpret_cast<uintptr_t>(g.minuend) | (uintptr_t)(g.ldm * 4)) % 32 == 0);
@@ -439,7 +521,11 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                 tmem_ld16(taddr, r);
                 if (!one_acc) tmem_ld16(taddr + acc_cols, q);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (!one_acc) {
+                if (F16) {                                           // hi * hi + (cross terms) / 2^11, and the operands' scales taken out
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        r[j] = __float_as_uint(__fmul_rn(__fmaf_rn(__uint_as_float(q[j]), 1.0f / kSplit16LoScale, __uint_as_float(r[j])), inv16));
+                } else if (!one_acc) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(q[j])));
                 }
@@ -509,15 +595,15 @@ bool tma_enabled() {
     return on;
 }
 
-size_t tma_smem_bytes(int n_tile, int nraw, int nr, int nb) {
-    return 1024 + (size_t)nraw * RAW_SLOT + (size_t)nr * A_SLOT + (size_t)nb * 2 * image_half_units(n_tile) * 16 + sizeof(TmaBars) + 64;
+size_t tma_smem_bytes(int n_tile, int nraw, int nr, int nb, bool f16 = false) {
+    return 1024 + (size_t)nraw * (f16 ? 2 : 1) * RAW_SLOT + (size_t)nr * A_SLOT + (size_t)nb * 2 * image_half_units(n_tile) * 16 + sizeof(TmaBars) + 64;
 }
 
-template <bool AK, int NMAX>
+template <bool AK, int NMAX, bool F16 = false>
 cudaError_t launch_tma(const CUtensorMap &map, const GemmArgs &g, dim3 grid, size_t smem, unsigned *status, cudaStream_t stream) {
-    cudaError_t err = cudaFuncSetAttribute(gemm_tc_tma_kernel<AK, NMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t err = cudaFuncSetAttribute(gemm_tc_tma_kernel<AK, NMAX, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return err;
-    gemm_tc_tma_kernel<AK, NMAX><<<grid, NTH, smem, stream>>>(map, g, status);
+    gemm_tc_tma_kernel<AK, NMAX, F16><<<grid, NTH, smem, stream>>>(map, g, status);
     return cudaGetLastError();
 }
 
@@ -525,8 +611,15 @@ cudaError_t launch_tma(const CUtensorMap &map, const GemmArgs &g, dim3 grid, siz
 
 // Ring lengths.  A contiguous along K: as many slots of A (split in place) as fit beside three images of B (four up to
 // 128 columns).  A contiguous along M: two operand stages, and as many raw slots as fit for the copies' head start.
-void gemm_tc_tma_rings(int n_tile, bool a_kmajor, int *nraw, int *nr, int *nb) {
+void gemm_tc_tma_rings(int n_tile, bool a_kmajor, int *nraw, int *nr, int *nb, bool f16) {
     *nb = n_tile > 128 ? 3 : 4;
+    if (f16) {                                             // raw boxes of 64 k (32 KB), operand stages, images of B
+        *nr = 2;
+        int r = 4;
+        while (r > 2 && tma_smem_bytes(n_tile, r, *nr, *nb, true) > (size_t)227 * 1024) --r;
+        *nraw = r;
+        return;
+    }
     if (a_kmajor) {
         int r = MAXR;
         while (r > 2 && tma_smem_bytes(n_tile, 0, r, *nb) > (size_t)227 * 1024) --r;
@@ -564,12 +657,13 @@ cudaError_t gemm_tc_tma_launch(const GemmArgs &g, bool a_kmajor, unsigned *statu
                        l2 == 256 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : (l2 == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_128B),
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
-    const size_t smem = tma_smem_bytes(g.n_tile, a_kmajor ? 0 : g.raw_stages, g.a_stages, g.b_stages);
+    const size_t smem = tma_smem_bytes(g.n_tile, (a_kmajor && !g.f16) ? 0 : g.raw_stages, g.a_stages, g.b_stages, g.f16);
     dim3 grid((g.M + TM - 1) / TM, (g.N + g.n_tile - 1) / g.n_tile, g.splits);
     if (g.persistent) {
         const int tiles = (int)(grid.x * grid.y);
         grid = dim3((unsigned)(tiles < g.sm_count ? tiles : g.sm_count), 1, 1);
     }
+    if (g.f16 && g.n_tile > 128) return a_kmajor ? launch_tma<true, 256, true>(map, g, grid, smem, status, stream) : launch_tma<false, 256, true>(map, g, grid, smem, status, stream);
     if (a_kmajor) return g.n_tile <= 128 ? launch_tma<true, 128>(map, g, grid, smem, status, stream) : launch_tma<true, 256>(map, g, grid, smem, status, stream);
     return g.n_tile <= 128 ? launch_tma<false, 128>(map, g, grid, smem, status, stream) : launch_tma<false, 256>(map, g, grid, smem, status, stream);
 }

@@ -80,12 +80,12 @@ bool topk_rows_fit_smem(const void *d_in, const void *d_residual, uint32_t cols,
 // word) receives kStatusBarrierTimeout if one of that kernel's bounded waits gives up.
 cudaError_t gemm(bool a_kmajor, bool b_kmajor, const float *A, long lda, const float *B, long ldb, float *C, long ldc, int M,
                  int N, int K, const float *kscale, const float *minuend, long ldm, unsigned *flag, unsigned *status,
-                 float *workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream);
+                 float *workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream, const unsigned *a_absmax_bits = nullptr);
 // The same with the kernel choice explicit: allow_tensor_cores = false keeps the product on the FP32 pipes.
 cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, const float *A, long lda, const float *B, long ldb,
                         float *C, long ldc, int M, int N, int K, const float *kscale, const float *minuend, long ldm,
                         unsigned *flag, unsigned *status, float *workspace, size_t workspace_bytes, int sm_count,
-                        cudaStream_t stream);
+                        cudaStream_t stream, const unsigned *a_absmax_bits = nullptr);
 
 struct SvdWorkspace;
 // sums `count` floats at `buf` over all ranks, enqueued on `stream`

@@ -59,6 +59,8 @@ struct SvdWorkspace {
     void *allreduce_ctx = nullptr;
     unsigned *status = nullptr;         // device status word of the current call
     unsigned *own_status = nullptr;     // used when the caller passes none
+    unsigned *a_absmax = nullptr;       // bits of the largest |A| of the current call (scale of the FP16 split of the big products)
+    bool a_absmax_valid = false;
     int jc_lanes = 4;                   // lanes per column pair of the cluster Jacobi kernel for this k
     bool jc_with_v = false;             // ... and whether it accumulates the right factor (else that comes from the panel)
     bool own_core_svd = false;          // k small enough for jacobi_svd_kernel (else cuSOLVER's gesvdj on the core)
@@ -1001,7 +1003,7 @@ cudaError_t times_w(SvdWorkspace *ws, const float *A, bool w_transposed_product,
     const long ldx = x_colmajor ? contract : ws->k;
     const int sp = span_begin(ws, 0, st);
     cudaError_t err = gemm(use_a_as_stored, x_colmajor, A, ws->n, X, ldx, C, ws->k, rows_out, ws->k, contract, nullptr,
-                           nullptr, 0, nullptr, ws->status, ws->gemm_ws, ws->gemm_ws_bytes, ws->sm_count, st);
+                           nullptr, 0, nullptr, ws->status, ws->gemm_ws, ws->gemm_ws_bytes, ws->sm_count, st, ws->a_absmax_valid ? ws->a_absmax : nullptr);
     span_end(ws, sp, st);
     // row-sharded W: W^T X contracts over the sharded rows, so the shards' partial products are summed
     if (err == cudaSuccess && w_transposed_product && ws->allreduce) err = timed_allreduce(ws, C, (size_t)rows_out * ws->k, st);
@@ -1041,6 +1043,7 @@ SvdWorkspace *svd_workspace_create_sharded(int m, int n, int k, int niter, int s
     ok = ok && alloc_f(&ws->gemm_ws, ws->gemm_ws_bytes / sizeof(float));
     ok = ok && cudaMalloc(reinterpret_cast<void **>(&ws->dev_info), sizeof(int)) == cudaSuccess;
     ok = ok && cudaMalloc(reinterpret_cast<void **>(&ws->own_status), sizeof(unsigned)) == cudaSuccess;
+    ok = ok && cudaMalloc(reinterpret_cast<void **>(&ws->a_absmax), sizeof(unsigned)) == cudaSuccess;
     ok = ok && curandCreateGenerator(&ws->rng, CURAND_RNG_PSEUDO_DEFAULT) == CURAND_STATUS_SUCCESS;
     ok = ok && cusolverDnCreate(&ws->solver) == CUSOLVER_STATUS_SUCCESS;
     ok = ok && cusolverDnCreateGesvdjInfo(&ws->svdj) == CUSOLVER_STATUS_SUCCESS;
@@ -1114,6 +1117,7 @@ void svd_workspace_destroy(SvdWorkspace *ws) {
         if (p) cudaFree(p);
     if (ws->dev_info) cudaFree(ws->dev_info);
     if (ws->own_status) cudaFree(ws->own_status);
+    if (ws->a_absmax) cudaFree(ws->a_absmax);
     for (cudaEvent_t e : ws->span_ev)
         if (e) cudaEventDestroy(e);
     if (ws->svdj) cusolverDnDestroyGesvdjInfo(ws->svdj);
@@ -1180,6 +1184,9 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
 
     cudaError_t err;
     float *q = nullptr, *qz = nullptr, *spare = nullptr;
+    // the largest |A|, once per call: the six products with A split it into FP16 halves scaled by a power of two from it
+    ws->a_absmax_valid = k > 128 && ws->n % 4 == 0 && reinterpret_cast<uintptr_t>(d_A) % 16 == 0 &&
+                         gemm_absmax_bits(d_A, ws->n, ws->m, ws->n, ws->a_absmax, st) == cudaSuccess;
     // Y = W Omega, Q = orth(Y).  Panels ping-pong between the two buffers of their size.
     if ((err = times_w(ws, d_A, false, ws->omega, true, ws->y, st)) != cudaSuccess) return err;
     const int last_passes = 2;
