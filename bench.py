@@ -577,6 +577,24 @@ def tf32_peak(torch):
         torch.backends.cuda.matmul.allow_tf32 = old
 
 
+def fp16_peak(torch):
+    """Dense FP16 rate of a library matrix product (FP32 accumulation), the denominator of the roofline when the products
+    run as three kind::f16 MMAs on operands split into FP16 halves: half matmul 8192^3, best of 10."""
+    a = torch.randn(8192, 8192, device="cuda").half()
+    b = torch.randn(8192, 8192, device="cuda").half()
+    for _ in range(3):
+        torch.matmul(a, b)
+    best = 1e9
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        torch.matmul(a, b)
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    return 2 * 8192 ** 3 / (best * 1e-3) / 1e12
+
+
 # ----------------------------------------------------------------------------------------------------------------
 # the bench line
 # ----------------------------------------------------------------------------------------------------------------
@@ -823,11 +841,14 @@ def main():
         prod_mean = statistics.mean(prod_ms) if prod_ms else None
         # products alternate: W X (W read along M: A as stored is K x M) and W^T X (A read along K)
         ach = flops / (prod_mean * 1e-3) / 1e12 if prod_mean else None
-        peak3 = tf32 / 3.0
+        # three MMAs per product either way: on FP16 halves (default) or on TF32 halves (BSQ_GEMM_F16=0)
+        split16 = os.environ.get("BSQ_GEMM_F16", "1") != "0"
+        fp16 = fp16_peak(torch) if split16 else None
+        peak3 = (fp16 if split16 else tf32) / 3.0
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": nsteps, "warmup": args.warmup,
             "ms_per_step": ms_total / nsteps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f32 (products as 3xTF32 on tcgen05, FP32-level accuracy)", "data": "synthetic",
+            "dtype": "f32 (products on tcgen05 from operands split into two FP16 halves with power-of-two scales, FP32-level accuracy)", "data": "synthetic",
             "config": {"workload": WORKLOAD, "rows": rows, "cols": cols, "layers": n_layers, "passes_per_step": passes,
                        "lanes_per_gpu": lanes, "passes_queued_together": mult,
                        "parallelism": "matrix i on rank i %% %d, no collective on the data path; %d matrices in flight per GPU" % (world, lanes),
@@ -850,9 +871,12 @@ def main():
                                              "returned host object, one matrix at a time, every call synchronous: the calls the "
                                              "reference arm makes"}},
             "gpu_launches": (LAUNCHES_PER_COMPRESS + LAUNCHES_PER_DECOMPRESS) * n_layers * passes * nsteps,
-            "roofline": {"bound": "tensor", "kernel": "gemm_tc_tma_kernel<*,256> (TMA-fed tcgen05 3xTF32, 4096x14336 matrix times a 256-column panel)",
+            "roofline": {"bound": "tensor", "kernel": "gemm_tc_tma_kernel<*,256> (TMA-fed tcgen05, operands split into two %s halves: three MMAs per "
+                                                       "product, 4096x14336 matrix times a 256-column panel)" % ("FP16" if split16 else "TF32"),
                          "achieved": ach, "peak": peak3, "unit": "TFLOP/s", "frac": (ach / peak3) if ach else None, "traffic": None,
-                         "peak_kind": "TF32 dense matmul measured in this run (%.0f TFLOP/s) / 3; BF16 %s %.0f" % (tf32, peak_kind, bf16_peak),
+                         "peak_kind": ("FP16 dense matmul measured in this run (%.0f TFLOP/s) / 3; TF32 dense measured %.0f (achieved / (TF32 / 3) = %.2f); BF16 %s %.0f"
+                                       % (fp16, tf32, (ach / (tf32 / 3.0)) if ach else 0.0, peak_kind, bf16_peak)) if split16 else
+                                      "TF32 dense matmul measured in this run (%.0f TFLOP/s) / 3; BF16 %s %.0f" % (tf32, peak_kind, bf16_peak),
                          "flops_per_launch": flops, "ms_per_launch": prod_mean, "launches_timed": len(prod_ms),
                          "ms_w_x": statistics.mean(prod_ms[0::2]) if prod_ms else None,
                          "ms_wt_x": statistics.mean(prod_ms[1::2]) if prod_ms else None,

@@ -601,6 +601,7 @@ int compress_begin(Runtime &rt, const float *x, int input_location, uint8_t *d_p
     // ---- stages ----
     const float *d_src = d_input;          // what SVD / the quantiser sees (outliers zeroed)
     bool fused_front = false;
+    bool residual_bound = false;                                        // d_status[8] holds an upper bound of |residual|
     if (!has_svd && rt.q_format != quantization_NONE && ko > 0 && !error_path && frontend_supported(rows, cols, ko) &&
         (reinterpret_cast<uintptr_t>(d_input) % 16) == 0) {
         fused_front = true;
@@ -610,8 +611,9 @@ int compress_begin(Runtime &rt, const float *x, int input_location, uint8_t *d_p
                               rt.sm_count, st) != cudaSuccess)
             return fail();
     } else if (ko > 0) {
+        // (the largest k-th |x| bounds what is left in the residual: the SVD's products take their FP16 scale from it)
         if (topk_rows(d_input, rt.residual.as<float>(), rows, cols, ko, rt.outlier.idx.as<uint16_t>(),
-                      rt.outlier.val.as<float>(), d_status, rt.sm_count, st) != cudaSuccess)
+                      rt.outlier.val.as<float>(), d_status, rt.sm_count, st, d_status + 8, &residual_bound) != cudaSuccess)
             return fail();
         d_src = rt.residual.as<float>();
     }
@@ -624,8 +626,8 @@ int compress_begin(Runtime &rt, const float *x, int input_location, uint8_t *d_p
         // can count on.  Every call here uses block 1: same singular values as that first reference call to ~5e-5
         // relative, and the same object for the same input on every call.
         const unsigned long long omega_offset = (unsigned long long)std::min(rows, cols) * rank;
-        if (svd_lowrank(rt.svd, d_src, rt.u.as<float>(), rt.s.as<float>(), rt.v.as<float>(), 1234ULL, d_status, st, omega_offset) !=
-            cudaSuccess)
+        if (svd_lowrank(rt.svd, d_src, rt.u.as<float>(), rt.s.as<float>(), rt.v.as<float>(), 1234ULL, d_status, st, omega_offset,
+                        residual_bound ? d_status + 8 : nullptr) != cudaSuccess)
             return fail();
         mark(); job.ev_svd = job.nev - 1;
         // quantised factors replace U, S, V in place for the error stage (src/bitsqz_llm.cu:1078-1139)

@@ -90,9 +90,13 @@ __device__ __forceinline__ void split_store(float4 v, float4 *hi, float4 *lo) {
 // in FP16's range (elements below 2^-28 of the largest lose bits, an absolute error below FP32's on the largest).
 // hi * hi goes into one accumulator, lo' * hi + hi * lo' into the other, which the epilogue scales by 2^-11.
 constexpr float kSplit16LoScale = 2048.0f;
-__device__ __forceinline__ float split16_scale(unsigned absmax_bits) {           // from the bits of the largest |x| (finite)
-    const int e = (int)((absmax_bits >> 23) & 0xFFu) - 127;
-    return absmax_bits == 0u ? 1.0f : exp2f((float)(14 - e));
+// The scale from the bits of the operand's largest |x|: 2^(14 - exponent), kept within 2^+-60 so that the product of
+// two scales and its reciprocal stay finite (an operand of zeros, or one that holds Inf / NaN, gets 1: zeros stay
+// zeros, and the non-finite values go through the conversion as they are).
+__device__ __forceinline__ float split16_scale(unsigned absmax_bits) {
+    if (absmax_bits == 0u || absmax_bits >= 0x7f800000u) return 1.0f;
+    const int e = (int)(absmax_bits >> 23) - 127;
+    return exp2f((float)min(max(14 - e, -60), 60));
 }
 // eight consecutive k of one row: two 16-byte units (hi, lo).  hi is taken as a float first, by the integer rounding
 // of tf32_rna (FP16 has TF32's 10 mantissa bits, so the value converts exactly wherever FP16 is normal), which leaves

@@ -39,8 +39,11 @@ int topk_num_columns(uint16_t cols, float ratio);
 // ranking below every number.  d_idx / d_val are [rows][k].  d_residual (nullable): receives
 // the row with the selected entries set to +0.0f; may alias d_in (in-place separation).
 // d_status: device word that receives kStatus* bits.
+// d_bound (nullable device word) receives, where the shared-memory path runs (*bound_written says so), the bits of the
+// largest k-th |x| over the rows: an upper bound of every |x| that is left in d_residual.
 cudaError_t topk_rows(const float *d_in, float *d_residual, uint32_t rows, uint32_t cols, uint32_t k, uint16_t *d_idx,
-                      float *d_val, unsigned *d_status, int sm_count, cudaStream_t stream);
+                      float *d_val, unsigned *d_status, int sm_count, cudaStream_t stream, unsigned *d_bound = nullptr,
+                      bool *bound_written = nullptr);
 
 // dense[row, idx] += val for every entry; indices >= cols are skipped and reported in d_status.
 cudaError_t topk_apply(const uint16_t *d_idx, const float *d_val, uint32_t rows, uint32_t cols, uint32_t k,
@@ -97,7 +100,10 @@ void svd_workspace_destroy(SvdWorkspace *ws);
 // A row-major m x n -> U (m x k row-major), S (k, descending), V (n x k row-major).
 // The random matrix is the first N x k normals of cuRAND's XORWOW sequence of `seed`, starting `offset` values in.
 cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d_S, float *d_V,
-                        unsigned long long seed, unsigned *d_status, cudaStream_t stream, unsigned long long offset = 0);
+                        unsigned long long seed, unsigned *d_status, cudaStream_t stream, unsigned long long offset = 0,
+                        const unsigned *d_abs_bound = nullptr);
+// (d_abs_bound, nullable: device word with the bits of an upper bound of |A|, e.g. from topk_rows; without it the call
+// makes a pass over A for the largest |A| where it needs one.)
 // Optional timing of a call's products with the big matrix (kind 0) and, row-sharded, its all-reduces (kind 1).
 cudaError_t svd_workspace_profile(SvdWorkspace *ws, bool on);
 int svd_workspace_spans(SvdWorkspace *ws, float *ms, int *kinds, int capacity);

@@ -61,6 +61,7 @@ struct SvdWorkspace {
     unsigned *own_status = nullptr;     // used when the caller passes none
     unsigned *a_absmax = nullptr;       // bits of the largest |A| of the current call (scale of the FP16 split of the big products)
     bool a_absmax_valid = false;
+    const unsigned *a_absmax_use = nullptr;
     int jc_lanes = 4;                   // lanes per column pair of the cluster Jacobi kernel for this k
     bool jc_with_v = false;             // ... and whether it accumulates the right factor (else that comes from the panel)
     bool own_core_svd = false;          // k small enough for jacobi_svd_kernel (else cuSOLVER's gesvdj on the core)
@@ -1003,7 +1004,7 @@ cudaError_t times_w(SvdWorkspace *ws, const float *A, bool w_transposed_product,
     const long ldx = x_colmajor ? contract : ws->k;
     const int sp = span_begin(ws, 0, st);
     cudaError_t err = gemm(use_a_as_stored, x_colmajor, A, ws->n, X, ldx, C, ws->k, rows_out, ws->k, contract, nullptr,
-                           nullptr, 0, nullptr, ws->status, ws->gemm_ws, ws->gemm_ws_bytes, ws->sm_count, st, ws->a_absmax_valid ? ws->a_absmax : nullptr);
+                           nullptr, 0, nullptr, ws->status, ws->gemm_ws, ws->gemm_ws_bytes, ws->sm_count, st, ws->a_absmax_valid ? ws->a_absmax_use : nullptr);
     span_end(ws, sp, st);
     // row-sharded W: W^T X contracts over the sharded rows, so the shards' partial products are summed
     if (err == cudaSuccess && w_transposed_product && ws->allreduce) err = timed_allreduce(ws, C, (size_t)rows_out * ws->k, st);
@@ -1161,7 +1162,7 @@ cudaError_t svd_workspace_finish(SvdWorkspace *ws, cudaStream_t st) {
 }
 
 cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d_S, float *d_V, unsigned long long seed,
-                        unsigned *d_status, cudaStream_t st, unsigned long long offset) {
+                        unsigned *d_status, cudaStream_t st, unsigned long long offset, const unsigned *d_abs_bound) {
     if (!ws || !d_A || !d_U || !d_S || !d_V) return cudaErrorInvalidValue;
     const int k = ws->k;
     ws->spans = 0;
@@ -1185,8 +1186,11 @@ cudaError_t svd_lowrank(SvdWorkspace *ws, const float *d_A, float *d_U, float *d
     cudaError_t err;
     float *q = nullptr, *qz = nullptr, *spare = nullptr;
     // the largest |A|, once per call: the six products with A split it into FP16 halves scaled by a power of two from it
-    ws->a_absmax_valid = k > 128 && ws->n % 4 == 0 && reinterpret_cast<uintptr_t>(d_A) % 16 == 0 &&
-                         gemm_absmax_bits(d_A, ws->n, ws->m, ws->n, ws->a_absmax, st) == cudaSuccess;
+    // (or a bound that the caller already has)
+    ws->a_absmax_use = d_abs_bound ? d_abs_bound : ws->a_absmax;
+    ws->a_absmax_valid = k > 128 && (d_abs_bound != nullptr ||
+                                     (ws->n % 4 == 0 && reinterpret_cast<uintptr_t>(d_A) % 16 == 0 &&
+                                      gemm_absmax_bits(d_A, ws->n, ws->m, ws->n, ws->a_absmax, st) == cudaSuccess));
     // Y = W Omega, Q = orth(Y).  Panels ping-pong between the two buffers of their size.
     if ((err = times_w(ws, d_A, false, ws->omega, true, ws->y, st)) != cudaSuccess) return err;
     const int last_passes = 2;

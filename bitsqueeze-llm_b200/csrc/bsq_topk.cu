@@ -26,7 +26,7 @@ template <int G>
 __global__ void __launch_bounds__(512)
     topk_rows_group_kernel(const float *__restrict__ in, float *residual, unsigned rows, unsigned cols, unsigned k,
                            uint16_t *__restrict__ out_idx, float *__restrict__ out_val, unsigned *status, unsigned group_bytes,
-                           unsigned ctl_off) {
+                           unsigned ctl_off, unsigned *bound) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const RowGroup<G> g;
     unsigned char *base = smem_raw + (size_t)g.gid * group_bytes;
@@ -73,6 +73,7 @@ __global__ void __launch_bounds__(512)
         };
         hint = group_topk_row<G>(g, c, row, cols, k, out_idx + (size_t)r * k, out_val + (size_t)r * k, residual != nullptr,
                                  hint, &special, row_free);
+        if (bound && g.lane == 0) atomicMax(bound, c.kth_bits);          // (published before the function's last group sync)
         fence_proxy_async_smem();
         g.sync();
         if (residual != nullptr && g.lane == 0) {
@@ -274,7 +275,7 @@ bool topk_rows_fit_smem(const void *d_in, const void *d_residual, uint32_t cols,
 
 template <int G>
 static cudaError_t launch_group(const float *d_in, float *d_residual, uint32_t rows, uint32_t cols, uint32_t k,
-                                uint16_t *d_idx, float *d_val, unsigned *d_status, int sm_count, cudaStream_t stream) {
+                                uint16_t *d_idx, float *d_val, unsigned *d_status, int sm_count, cudaStream_t stream, unsigned *d_bound) {
     const GroupGeometry f = group_geometry(cols);
     const size_t smem = (size_t)f.group_bytes * f.groups;
     cudaError_t err = cudaFuncSetAttribute(topk_rows_group_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -290,12 +291,13 @@ static cudaError_t launch_group(const float *d_in, float *d_residual, uint32_t r
     const unsigned needed = (rows + f.groups - 1) / f.groups;
     if (grid > needed) grid = needed;
     topk_rows_group_kernel<G><<<grid, f.threads, smem, stream>>>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status,
-                                                                  f.group_bytes, f.ctl_off);
+                                                                  f.group_bytes, f.ctl_off, d_bound);
     return cudaGetLastError();
 }
 
 cudaError_t topk_rows(const float *d_in, float *d_residual, uint32_t rows, uint32_t cols, uint32_t k, uint16_t *d_idx,
-                      float *d_val, unsigned *d_status, int sm_count, cudaStream_t stream) {
+                      float *d_val, unsigned *d_status, int sm_count, cudaStream_t stream, unsigned *d_bound, bool *bound_written) {
+    if (bound_written) *bound_written = false;
     if (!d_in || rows == 0 || cols == 0 || cols > 65535u || k > cols) return cudaErrorInvalidValue;
     if (k == 0) {
         if (d_residual && d_residual != d_in)
@@ -304,10 +306,15 @@ cudaError_t topk_rows(const float *d_in, float *d_residual, uint32_t rows, uint3
     }
     if (!d_idx || !d_val) return cudaErrorInvalidValue;
     if (topk_rows_fit_smem(d_in, d_residual, cols, k)) {
+        if (d_bound) {
+            const cudaError_t e = cudaMemsetAsync(d_bound, 0, sizeof(unsigned), stream);
+            if (e != cudaSuccess) return e;
+            if (bound_written) *bound_written = true;
+        }
         switch (group_geometry(cols).G) {
-            case 2: return launch_group<2>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status, sm_count, stream);
-            case 4: return launch_group<4>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status, sm_count, stream);
-            default: return launch_group<8>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status, sm_count, stream);
+            case 2: return launch_group<2>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status, sm_count, stream, d_bound);
+            case 4: return launch_group<4>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status, sm_count, stream, d_bound);
+            default: return launch_group<8>(d_in, d_residual, rows, cols, k, d_idx, d_val, d_status, sm_count, stream, d_bound);
         }
     }
     unsigned grid = (unsigned)sm_count * 8u;
