@@ -84,6 +84,7 @@ SIGNATURES = {
     "bsq_svd_lowrank_at": (_i, [_vp, _i, _i, _i, _i, C.c_ulonglong, C.c_ulonglong, _vp, _vp, _vp, _vp]),
     "bsq_reconstruct": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "bsq_gemm": (_i, [_i, _i, _vp, C.c_long, _vp, C.c_long, _vp, C.c_long, _i, _i, _i, _vp, _sz, _i, _vp, _vp]),
+    "bsq_gemm_bounded": (_i, [_i, _i, _vp, C.c_long, _vp, C.c_long, _vp, C.c_long, _i, _i, _i, _vp, _sz, _vp, _vp, _vp]),
     "bsq_shard_unique_id": (_i, [_vp, _sz]),
     "bsq_shard_comm_create": (_vp, [_vp, _i, _i]),
     "bsq_shard_comm_destroy": (None, [_vp]),

@@ -149,6 +149,13 @@ int bsq_gemm(int a_kmajor, int b_kmajor, const float *d_A, long lda, const float
     return rc(gemm_select(allow_tensor_cores != 0, a_kmajor != 0, b_kmajor != 0, d_A, lda, d_B, ldb, d_C, ldc, M, N, K, nullptr,
                           nullptr, 0, nullptr, d_status, d_workspace, workspace_bytes, device_sm_count(), as_stream(stream)));
 }
+int bsq_gemm_bounded(int a_kmajor, int b_kmajor, const float *d_A, long lda, const float *d_B, long ldb, float *d_C, long ldc, int M,
+                     int N, int K, float *d_workspace, size_t workspace_bytes, const uint32_t *d_a_absmax_bits, uint32_t *d_status,
+                     void *stream) {
+    if (!d_A || !d_B || !d_C || !d_a_absmax_bits || M <= 0 || N <= 0 || K <= 0) return 1;
+    return rc(gemm_select(true, a_kmajor != 0, b_kmajor != 0, d_A, lda, d_B, ldb, d_C, ldc, M, N, K, nullptr, nullptr, 0, nullptr,
+                          d_status, d_workspace, workspace_bytes, device_sm_count(), as_stream(stream), d_a_absmax_bits));
+}
 int bsq_reconstruct(const float *d_U, const float *d_S, const float *d_V, int m, int n, int k, const float *d_minuend,
                     float *d_out, uint32_t *d_flag, uint32_t *d_status, void *stream) {
     if (!d_U || !d_S || !d_V || !d_out || m <= 0 || n <= 0 || k <= 0) return 1;

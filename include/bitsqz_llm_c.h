@@ -148,6 +148,15 @@ int bsq_reconstruct(const float *d_U, const float *d_S, const float *d_V, int m,
 int bsq_gemm(int a_kmajor, int b_kmajor, const float *d_A, long lda, const float *d_B, long ldb, float *d_C, long ldc, int M,
              int N, int K, float *d_workspace, size_t workspace_bytes, int allow_tensor_cores, uint32_t *d_status, void *stream);
 
+/* The same product when the caller knows an upper bound of |A| (a device word holding the bits of a finite, non-negative
+ * float): 256-column products on the TMA-fed kernel then split their operands into two FP16 halves, scaled by powers of
+ * two taken from that bound and from the largest |B|, instead of two TF32 halves (same accuracy class, twice the
+ * tensor rate); every other shape runs as in bsq_gemm.  A bound below the true maximum overflows FP16: the result
+ * holds Inf / NaN then. */
+int bsq_gemm_bounded(int a_kmajor, int b_kmajor, const float *d_A, long lda, const float *d_B, long ldb, float *d_C, long ldc, int M,
+                     int N, int K, float *d_workspace, size_t workspace_bytes, const uint32_t *d_a_absmax_bits, uint32_t *d_status,
+                     void *stream);
+
 /* ---- row-sharded SVD over several GPUs, one process per GPU (no counterpart in the reference, which is
  * single-GPU; the sharded form of svd_lowrank_cuda, svd_lowrank_cuda.cuh:54-68).  A is split by rows; each
  * rank passes its m_local x n slice and receives its rows of U; S and V are replicated and bit-identical

@@ -86,3 +86,43 @@ def test_gemm_with_b_split_beforehand_for_every_shape():
                           "-k", "test_gemm_matches_fp64 or test_gemm_tensor_core_path_is_repeatable"],
                          env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+
+
+@pytest.mark.parametrize("a_kmajor,b_kmajor", [(1, 0), (1, 1), (0, 0), (0, 1)])
+@pytest.mark.parametrize("scale_log2", [0, 40, -40])
+def test_gemm_fp16_halves_match_fp64_and_follow_the_scale(lib, a_kmajor, b_kmajor, scale_log2):
+    """256-column products with a caller-supplied bound on |A| split their operands into two FP16 halves with
+    power-of-two scales (bsq_gemm_bounded).  Same tolerance against FP64 as the TF32 halves; scaling A by a power of two
+    must scale the result by exactly that power (the split sees the same halves); a bound above the true maximum is
+    allowed."""
+    M, N, K = 1024, 256, 2048
+    a, b = operands(M, N, K, a_kmajor, b_kmajor, 5)
+    ws = torch.zeros(64 << 20, dtype=torch.uint8, device="cuda")
+
+    def run_bounded(a_op, bound):
+        c = torch.full((M, N), float("nan"), device="cuda", dtype=torch.float32)
+        st = torch.zeros(1, dtype=torch.int32, device="cuda")
+        word = torch.tensor([bound], dtype=torch.float32, device="cuda")
+        rc = lib.bsq_gemm_bounded(int(a_kmajor), int(b_kmajor), a_op.data_ptr(), a_op.shape[1], b.data_ptr(), b.shape[1], c.data_ptr(), N,
+                                  M, N, K, ws.data_ptr(), ws.numel(), word.data_ptr(), st.data_ptr(), None)
+        torch.cuda.synchronize()
+        assert rc == 0 and int(st.item()) == 0
+        return c
+    base = run_bounded(a, float(a.abs().max()))
+    want, mag = product_fp64(a, b, a_kmajor, b_kmajor)
+    # 22 significant bits per operand element, FP32 accumulation: a few 1e-6 of sum |a||b|
+    assert float(((base.double() - want).abs() / mag).max()) <= 4e-6
+    f = float(2.0 ** scale_log2)
+    scaled = run_bounded(a * f, float(a.abs().max()) * f * 1.7)        # (a bound that is not tight)
+    assert torch.equal(scaled, base * f)
+    # elements far below the largest still count: rows of A shrunk by 2^-20 give rows of C shrunk alike, to FP32 accuracy
+    a2 = a.clone()
+    rows = slice(0, 64)
+    if a_kmajor:
+        a2[rows, :] *= 2.0 ** -20
+    else:
+        a2[:, rows] *= 2.0 ** -20
+    small = run_bounded(a2, float(a2.abs().max()))
+    # (this is the FP16 path: a bound 2^6 below the true maximum leaves FP16's range, and the result says so)
+    assert not bool(torch.isfinite(run_bounded(a, float(a.abs().max()) / 64.0)).all())
+    assert float(((small[rows].double() - want[rows] * 2.0 ** -20).abs() / (mag[rows] * 2.0 ** -20)).max()) <= 2e-5
