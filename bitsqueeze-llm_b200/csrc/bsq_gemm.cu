@@ -247,15 +247,15 @@ size_t gemm_workspace_bytes(int M, int N, int max_splits) { return (size_t)M * N
 // Picks the K split so that about two CTAs per SM are busy; partials go to `workspace` (may be null: no split).
 cudaError_t gemm(bool a_kmajor, bool b_kmajor, const float *A, long lda, const float *B, long ldb, float *C, long ldc, int M,
                  int N, int K, const float *kscale, const float *minuend, long ldm, unsigned *flag, unsigned *status,
-                 float *workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream, const unsigned *a_absmax_bits) {
+                 float *workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream, const unsigned *a_absmax_bits, float b_bound) {
     return gemm_select(tensor_cores_enabled(), a_kmajor, b_kmajor, A, lda, B, ldb, C, ldc, M, N, K, kscale, minuend, ldm, flag,
-                       status, workspace, workspace_bytes, sm_count, stream, a_absmax_bits);
+                       status, workspace, workspace_bytes, sm_count, stream, a_absmax_bits, b_bound);
 }
 
 cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, const float *A, long lda, const float *B, long ldb,
                         float *C, long ldc, int M, int N, int K, const float *kscale, const float *minuend, long ldm,
                         unsigned *flag, unsigned *status, float *workspace, size_t workspace_bytes, int sm_count,
-                        cudaStream_t stream, const unsigned *a_absmax_bits) {
+                        cudaStream_t stream, const unsigned *a_absmax_bits, float b_bound) {
     if (M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
     if (allow_tensor_cores) {
         // tensor-core path: one 128-row tile per CTA, two CTAs per SM up to N = 128; K is split so that the tiles fill
@@ -322,6 +322,7 @@ cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, c
             workspace_bytes -= 256;
             t.f16 = true;
             t.b_absmax_bits = words;
+            if (b_bound > 0.0f && b_bound < 1.0e30f) t.b_scale_fixed = std::exp2((float)(14 - std::ilogb(b_bound)));
             t.a_absmax_bits = a_absmax_bits;
             if (!a_absmax_bits) {
                 const cudaError_t e = gemm_absmax_bits(A, lda, a_kmajor ? M : K, a_kmajor ? K : M, words + 1, stream);

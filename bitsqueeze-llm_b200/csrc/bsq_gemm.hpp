@@ -37,6 +37,7 @@ struct GemmArgs {
     bool f16;                      // TMA-fed kernel: operands split into two FP16 halves (bsq_gemm_tc.cuh) instead of two TF32
     const unsigned *a_absmax_bits; // halves; device words with the bits of the largest |A| and |B| (finite), from which the
     const unsigned *b_absmax_bits; // power-of-two scales of the split come
+    float b_scale_fixed;           // > 0: the scale of B given by the caller (from a bound it knows) instead of *b_absmax_bits
 };
 
 // Tensor-core path: true if the shape qualifies (N a multiple of 16, 16-byte aligned operands with leading

@@ -528,7 +528,7 @@ __global__ void __launch_bounds__(256) absmax_bits_kernel(const float *__restric
 // as the TF32 images, which hold 16 k per chunk).  k past K gives zeros.
 template <bool B_KMAJOR>
 __global__ void __launch_bounds__(256) presplit_b16_kernel(const float *__restrict__ B, long ldb, int N, int K, int n_tile, int chunks,
-                                                           uint4 *__restrict__ image, const unsigned *__restrict__ absmax_bits) {
+                                                           uint4 *__restrict__ image, const unsigned *__restrict__ absmax_bits, float fixed_scale) {
     const int n0 = blockIdx.y * n_tile;
     const int Nt = min(n_tile, N - n0);
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -561,7 +561,7 @@ __global__ void __launch_bounds__(256) presplit_b16_kernel(const float *__restri
     }
     uint4 *img = image + ((size_t)blockIdx.y * chunks + c) * image_units(n_tile);
     const unsigned u = image_unit_index(kc, r, Nt);
-    split16_store8(make_float4(v[0], v[1], v[2], v[3]), make_float4(v[4], v[5], v[6], v[7]), split16_scale(*absmax_bits), img + u,
+    split16_store8(make_float4(v[0], v[1], v[2], v[3]), make_float4(v[4], v[5], v[6], v[7]), fixed_scale > 0.0f ? fixed_scale : split16_scale(*absmax_bits), img + u,
                    img + image_half_units(Nt) + u);
 }
 
@@ -750,13 +750,16 @@ cudaError_t launch_image(const GemmArgs &g, bool b_kmajor, unsigned *status, cud
     cudaError_t err;
     if (g.f16) {
         // the scale of B's split comes from its largest magnitude (B is a panel: a pass over it costs microseconds)
+        // (unless the caller knows a bound: FP16 is floating point, so a loose bound costs range, not precision)
         unsigned *bmax = const_cast<unsigned *>(g.b_absmax_bits);
-        if ((err = cudaMemsetAsync(bmax, 0, sizeof(unsigned), stream)) != cudaSuccess) return err;
-        const int b_rows = b_kmajor ? g.N : g.K, b_cols = b_kmajor ? g.K : g.N;
-        absmax_bits_kernel<<<296, 256, 0, stream>>>(g.B, g.ldb, b_rows, b_cols, bmax);
+        if (!(g.b_scale_fixed > 0.0f)) {
+            if ((err = cudaMemsetAsync(bmax, 0, sizeof(unsigned), stream)) != cudaSuccess) return err;
+            const int b_rows = b_kmajor ? g.N : g.K, b_cols = b_kmajor ? g.K : g.N;
+            absmax_bits_kernel<<<296, 256, 0, stream>>>(g.B, g.ldb, b_rows, b_cols, bmax);
+        }
         uint4 *image16 = reinterpret_cast<uint4 *>(image);
-        if (b_kmajor) presplit_b16_kernel<true><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image16, bmax);
-        else presplit_b16_kernel<false><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image16, bmax);
+        if (b_kmajor) presplit_b16_kernel<true><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image16, bmax, g.b_scale_fixed);
+        else presplit_b16_kernel<false><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image16, bmax, g.b_scale_fixed);
     } else if (b_kmajor) presplit_b_kernel<true><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image);
     else presplit_b_kernel<false><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image);
     err = cudaGetLastError();

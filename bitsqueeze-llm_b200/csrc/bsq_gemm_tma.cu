@@ -448,7 +448,7 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
         // ---- epilogue: this thread's accumulator row of every tile, 16 columns at a time ----
         const int quarter = warp & 3;                                    // the tensor-memory lanes this warp may read
         const int cb = (one_acc && warp < 7) ? 128 : 0;                  // wide tiles: first column of this warp's half of the tile
-        const float inv16 = F16 ? 1.0f / (split16_scale(*g.a_absmax_bits) * split16_scale(*g.b_absmax_bits)) : 1.0f;
+        const float inv16 = F16 ? 1.0f / (split16_scale(*g.a_absmax_bits) * (g.b_scale_fixed > 0.0f ? g.b_scale_fixed : split16_scale(*g.b_absmax_bits))) : 1.0f;
         // 32-byte accesses need 32-byte aligned rows of C and of the minuend (tile columns start at multiples of 16)
         const bool wide32 = ((reinterpret_cast<uintptr_t>(g.C) | (uintptr_t)(g.ldc * 4) | (uintptr_t)(g.split_stride * 4)) % 32 == 0) &&
                             (!g.minuend || (reinterpret_cast<uintptr_t>(g.minuend) | (uintptr_t)(g.ldm * 4)) % 32 == 0);

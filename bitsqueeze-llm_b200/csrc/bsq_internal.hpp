@@ -83,12 +83,15 @@ bool topk_rows_fit_smem(const void *d_in, const void *d_residual, uint32_t cols,
 // word) receives kStatusBarrierTimeout if one of that kernel's bounded waits gives up.
 cudaError_t gemm(bool a_kmajor, bool b_kmajor, const float *A, long lda, const float *B, long ldb, float *C, long ldc, int M,
                  int N, int K, const float *kscale, const float *minuend, long ldm, unsigned *flag, unsigned *status,
-                 float *workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream, const unsigned *a_absmax_bits = nullptr);
+                 float *workspace, size_t workspace_bytes, int sm_count, cudaStream_t stream, const unsigned *a_absmax_bits = nullptr,
+                 float b_bound = 0.0f);
 // The same with the kernel choice explicit: allow_tensor_cores = false keeps the product on the FP32 pipes.
 cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, const float *A, long lda, const float *B, long ldb,
                         float *C, long ldc, int M, int N, int K, const float *kscale, const float *minuend, long ldm,
                         unsigned *flag, unsigned *status, float *workspace, size_t workspace_bytes, int sm_count,
-                        cudaStream_t stream, const unsigned *a_absmax_bits = nullptr);
+                        cudaStream_t stream, const unsigned *a_absmax_bits = nullptr, float b_bound = 0.0f);
+// (a_absmax_bits: device word with the bits of an upper bound of |A|, b_bound: an upper bound of |B| known on the host,
+// 0 = none -- with a bound on |A| the 256-column products split their operands into FP16 halves, bsq_gemm_tc.cuh)
 
 struct SvdWorkspace;
 // sums `count` floats at `buf` over all ranks, enqueued on `stream`

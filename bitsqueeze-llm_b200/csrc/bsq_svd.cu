@@ -1004,7 +1004,10 @@ cudaError_t times_w(SvdWorkspace *ws, const float *A, bool w_transposed_product,
     const long ldx = x_colmajor ? contract : ws->k;
     const int sp = span_begin(ws, 0, st);
     cudaError_t err = gemm(use_a_as_stored, x_colmajor, A, ws->n, X, ldx, C, ws->k, rows_out, ws->k, contract, nullptr,
-                           nullptr, 0, nullptr, ws->status, ws->gemm_ws, ws->gemm_ws_bytes, ws->sm_count, st, ws->a_absmax_valid ? ws->a_absmax_use : nullptr);
+                           nullptr, 0, nullptr, ws->status, ws->gemm_ws, ws->gemm_ws_bytes, ws->sm_count, st, ws->a_absmax_valid ? ws->a_absmax_use : nullptr,
+                           // what X can hold: standard normal draws from 32-bit uniforms stay below 6.7, the columns of an
+                           // orthonormalised panel have norm 1 (a loose bound costs FP16 range, not precision)
+                           x_colmajor ? 16.0f : 1024.0f);
     span_end(ws, sp, st);
     // row-sharded W: W^T X contracts over the sharded rows, so the shards' partial products are summed
     if (err == cudaSuccess && w_transposed_product && ws->allreduce) err = timed_allreduce(ws, C, (size_t)rows_out * ws->k, st);
