@@ -52,3 +52,20 @@ def test_cmake_consumer_builds_and_runs(built, tmp_path):
     run = subprocess.run([str(build / "consumer")], capture_output=True, text=True)
     assert run.returncode == 0, (run.returncode, run.stdout, run.stderr)
     assert "sm_100a" in run.stdout
+
+
+def test_row_slices_of_the_sharded_workload_agree():
+    """The row shards of the tall matrix (bench.py's row-sharded leg) are slices of ONE matrix: whatever the number of
+    ranks, a row must get the same values (the leg's 8-rank parity run slices 32768 rows into 4096-row shards)."""
+    torch = pytest.importorskip("torch")
+    import importlib
+    W = importlib.import_module("bitsqueeze-llm_b200.workloads")
+    rows, cols, band = 4 * W.SLICE_BAND, 128, W.SLICE_BAND
+    whole = W.lowrank_matrix(torch, rows, cols, 7, components=32, device="cpu", row_slice=(0, rows))
+    for ranks in (2, 4):
+        per = rows // ranks
+        parts = [W.lowrank_matrix(torch, rows, cols, 7, components=32, device="cpu", row_slice=(r * per, per)) for r in range(ranks)]
+        assert torch.equal(torch.cat(parts), whole)
+    for bad in ((1, band), (0, band + 1), (rows, band), (0, 0)):
+        with pytest.raises(ValueError):
+            W.lowrank_matrix(torch, rows, cols, 7, components=32, device="cpu", row_slice=bad)
