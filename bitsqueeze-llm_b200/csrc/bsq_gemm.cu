@@ -308,6 +308,16 @@ cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, c
                     if (wide_tiles_enabled()) {
                         t.n_tile = 256;                                 // (B's images were given room for 256-column tiles above)
                         t.wide_tiles = true;
+                        // ... and both operands as FP16 halves (low halves without their factor: the tile's products share
+                        // one accumulator); the scales come from the largest |A kscale| and |B|, found by a pass over each
+                        // (they are small); the FP16 images take half the room, its last words hold the two maxima
+                        if (f16_mode() >= 1 && K % 8 == 0) {
+                            unsigned *words = reinterpret_cast<unsigned *>(reinterpret_cast<unsigned char *>(workspace) + a_room - 256);
+                            t.f16 = true;
+                            t.lo_unscaled = true;
+                            t.a_absmax_bits = words;
+                            t.b_absmax_bits = words + 1;
+                        }
                     }
                 }
             }
@@ -330,7 +340,7 @@ cudaError_t gemm_select(bool allow_tensor_cores, bool a_kmajor, bool b_kmajor, c
                 t.a_absmax_bits = words + 1;
             }
         }
-        if (t.use_tma) gemm_tc_tma_rings(t.n_tile, a_kmajor, &t.raw_stages, &t.a_stages, &t.b_stages, t.f16);
+        if (t.use_tma) gemm_tc_tma_rings(t.n_tile, a_kmajor, &t.raw_stages, &t.a_stages, &t.b_stages, t.f16 && !t.a_image);
         else if (with_image) gemm_tc_image_rings(t.n_tile, &t.a_stages, &t.b_stages);
         if (workspace && !minuend && !kscale && tiles_tc < slots) {
             const int max_by_k = max(1, K / 256);             // a split below 256 of K costs more in the reduction than it gains

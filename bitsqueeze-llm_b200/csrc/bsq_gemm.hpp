@@ -38,6 +38,9 @@ struct GemmArgs {
     const unsigned *a_absmax_bits; // halves; device words with the bits of the largest |A| and |B| (finite), from which the
     const unsigned *b_absmax_bits; // power-of-two scales of the split come
     float b_scale_fixed;           // > 0: the scale of B given by the caller (from a bound it knows) instead of *b_absmax_bits
+    bool lo_unscaled;              // the low halves are fp16(x s - hi) without the factor 2^11, so that all three products of a
+                                   // term can share ONE accumulator (the persistent product's 256-column tiles); elements more
+                                   // than 2^18 below the operand's largest then lose bits of their low half
 };
 
 // Tensor-core path: true if the shape qualifies (N a multiple of 16, 16-byte aligned operands with leading

@@ -512,11 +512,16 @@ __global__ void __launch_bounds__(256) presplit_a_kernel(const float *__restrict
 // The largest |x| of a rows x cols matrix (leading dimension ld) as float bits, by atomicMax into *out (cleared by the
 // caller).  Non-finite values leave bits >= 0x7f800000 there, which split16_scale answers with... a scale that no
 // longer matters: the product is NaN or Inf then, as it is for the reference.
-__global__ void __launch_bounds__(256) absmax_bits_kernel(const float *__restrict__ x, long ld, int rows, int cols, unsigned *out) {
+__global__ void __launch_bounds__(256) absmax_bits_kernel(const float *__restrict__ x, long ld, int rows, int cols, unsigned *out,
+                                                          const float *__restrict__ colscale = nullptr) {
     const int c4 = cols / 4;
     unsigned m = 0;
     for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < (long)rows * c4; e += (long)gridDim.x * blockDim.x) {
-        const float4 v = *reinterpret_cast<const float4 *>(x + (e / c4) * ld + (e % c4) * 4);
+        float4 v = *reinterpret_cast<const float4 *>(x + (e / c4) * ld + (e % c4) * 4);
+        if (colscale) {
+            const int c = (int)(e % c4) * 4;
+            v.x *= colscale[c]; v.y *= colscale[c + 1]; v.z *= colscale[c + 2]; v.w *= colscale[c + 3];
+        }
         m = max(max(m, __float_as_uint(v.x) & 0x7fffffffu), max(__float_as_uint(v.y) & 0x7fffffffu, max(__float_as_uint(v.z) & 0x7fffffffu, __float_as_uint(v.w) & 0x7fffffffu)));
     }
     m = __reduce_max_sync(0xffffffffu, m);
@@ -528,7 +533,8 @@ __global__ void __launch_bounds__(256) absmax_bits_kernel(const float *__restric
 // as the TF32 images, which hold 16 k per chunk).  k past K gives zeros.
 template <bool B_KMAJOR>
 __global__ void __launch_bounds__(256) presplit_b16_kernel(const float *__restrict__ B, long ldb, int N, int K, int n_tile, int chunks,
-                                                           uint4 *__restrict__ image, const unsigned *__restrict__ absmax_bits, float fixed_scale) {
+                                                           uint4 *__restrict__ image, const unsigned *__restrict__ absmax_bits, float fixed_scale,
+                                                           float lo_scale) {
     const int n0 = blockIdx.y * n_tile;
     const int Nt = min(n_tile, N - n0);
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -562,7 +568,29 @@ __global__ void __launch_bounds__(256) presplit_b16_kernel(const float *__restri
     uint4 *img = image + ((size_t)blockIdx.y * chunks + c) * image_units(n_tile);
     const unsigned u = image_unit_index(kc, r, Nt);
     split16_store8(make_float4(v[0], v[1], v[2], v[3]), make_float4(v[4], v[5], v[6], v[7]), fixed_scale > 0.0f ? fixed_scale : split16_scale(*absmax_bits), img + u,
-                   img + image_half_units(Nt) + u);
+                   img + image_half_units(Nt) + u, lo_scale);
+}
+
+// The FP16 form of presplit_a_kernel: two row-major rows_pad x K matrices of FP16 values, hi then lo, eight k per thread;
+// the scale comes from *absmax_bits, the largest |A(m, k) kscale(k)| (absmax_bits_kernel with the same kscale).
+__global__ void __launch_bounds__(256) presplit_a16_kernel(const float *__restrict__ A, long lda, int M, int K, const float *__restrict__ kscale,
+                                                           uint4 *__restrict__ image, int rows_pad, const unsigned *__restrict__ absmax_bits,
+                                                           float lo_scale) {
+    const int k8 = K / 8;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)rows_pad * k8) return;
+    const int m = (int)(idx / k8), k = (int)(idx % k8) * 8;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+    if (m < M) {
+        a = *reinterpret_cast<const float4 *>(A + (long)m * lda + k);
+        b = *reinterpret_cast<const float4 *>(A + (long)m * lda + k + 4);
+        if (kscale) {
+            a.x *= kscale[k]; a.y *= kscale[k + 1]; a.z *= kscale[k + 2]; a.w *= kscale[k + 3];
+            b.x *= kscale[k + 4]; b.y *= kscale[k + 5]; b.z *= kscale[k + 6]; b.w *= kscale[k + 7];
+        }
+    }
+    uint4 *hi = image + idx;
+    split16_store8(a, b, split16_scale(*absmax_bits), hi, hi + (long)rows_pad * k8, lo_scale);
 }
 
 template <bool A_KMAJOR, int NMAX>
@@ -758,13 +786,23 @@ cudaError_t launch_image(const GemmArgs &g, bool b_kmajor, unsigned *status, cud
             absmax_bits_kernel<<<296, 256, 0, stream>>>(g.B, g.ldb, b_rows, b_cols, bmax);
         }
         uint4 *image16 = reinterpret_cast<uint4 *>(image);
-        if (b_kmajor) presplit_b16_kernel<true><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image16, bmax, g.b_scale_fixed);
-        else presplit_b16_kernel<false><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image16, bmax, g.b_scale_fixed);
+        const float lo_scale = g.lo_unscaled ? 1.0f : kSplit16LoScale;
+        if (b_kmajor) presplit_b16_kernel<true><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image16, bmax, g.b_scale_fixed, lo_scale);
+        else presplit_b16_kernel<false><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image16, bmax, g.b_scale_fixed, lo_scale);
     } else if (b_kmajor) presplit_b_kernel<true><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image);
     else presplit_b_kernel<false><<<pgrid, 256, 0, stream>>>(g.B, g.ldb, g.N, g.K, g.n_tile, chunks, image);
     err = cudaGetLastError();
     if (err != cudaSuccess) return err;
-    if (g.use_tma && g.a_image) {
+    if (g.use_tma && g.a_image && g.f16) {
+        // the largest |A kscale| for the scale, then the two FP16 matrices
+        unsigned *amax = const_cast<unsigned *>(g.a_absmax_bits);
+        if ((err = cudaMemsetAsync(amax, 0, sizeof(unsigned), stream)) != cudaSuccess) return err;
+        absmax_bits_kernel<<<296, 256, 0, stream>>>(g.A, g.lda, g.M, g.K, amax, g.kscale);
+        const long units = (long)g.a_image_rows * (g.K / 8);
+        presplit_a16_kernel<<<(unsigned)((units + 255) / 256), 256, 0, stream>>>(g.A, g.lda, g.M, g.K, g.kscale, reinterpret_cast<uint4 *>(g.a_image),
+                                                                                  g.a_image_rows, amax, g.lo_unscaled ? 1.0f : kSplit16LoScale);
+        if ((err = cudaGetLastError()) != cudaSuccess) return err;
+    } else if (g.use_tma && g.a_image) {
         const long quads = (long)g.a_image_rows * (g.K / 4);
         presplit_a_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, stream>>>(g.A, g.lda, g.M, g.K, g.kscale, g.a_image, g.a_image_rows);
         if ((err = cudaGetLastError()) != cudaSuccess) return err;

@@ -101,14 +101,14 @@ __device__ __forceinline__ float split16_scale(unsigned absmax_bits) {
 // eight consecutive k of one row: two 16-byte units (hi, lo).  hi is taken as a float first, by the integer rounding
 // of tf32_rna (FP16 has TF32's 10 mantissa bits, so the value converts exactly wherever FP16 is normal), which leaves
 // one conversion instruction per pair of halves (cvt.rn.f16x2.f32) instead of three conversions per element.
-__device__ __forceinline__ void split16_store8(const float4 &a, const float4 &b, float s, uint4 *hi, uint4 *lo) {
+__device__ __forceinline__ void split16_store8(const float4 &a, const float4 &b, float s, uint4 *hi, uint4 *lo, float lo_scale = kSplit16LoScale) {
     const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
     float h[8], l[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const float xs = v[i] * s;
         h[i] = tf32_rna(xs);
-        l[i] = (xs - h[i]) * kSplit16LoScale;
+        l[i] = (xs - h[i]) * lo_scale;
     }
     auto pack = [](float p, float q) {
         const __half2 r = __floats2half2_rn(p, q);

@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
     constexpr int TK = F16 ? 32 : bsq::TK;                 // K per image of B
     constexpr bool USES_RAW = !A_KMAJOR || F16;
     constexpr unsigned RAW_SLOT = F16 ? 2u * bsq::RAW_SLOT : bsq::RAW_SLOT;
-    const int NR = g.a_stages, NB = g.b_stages, NRAW = USES_RAW ? g.raw_stages : 0;
+    const int NR = g.a_stages, NB = g.b_stages, NRAW = (USES_RAW && g.a_image == nullptr) ? g.raw_stages : 0;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool a_img = A_KMAJOR && g.a_image != nullptr;           // A split beforehand: both halves of a slot come in by TMA
     const unsigned b_stride = 2u * image_half_units(g.n_tile) * 16u;
@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
         // ---- A producer: one box per slot, as far ahead as the ring allows ----
         if (lane == 0) {
             int ca = 0;                                                  // slots filled so far, over all tiles
-            Ring ra(USES_RAW ? NRAW : NR);
+            Ring ra((USES_RAW && !a_img) ? NRAW : NR);
             for (int i = 0; i < walk.count && ok; ++i) {
                 int mt, nt, z;
                 walk.at(i, &mt, &nt, &z);
@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                 const int chunks_a = (k_end - k_begin + KS - 1) / KS;
                 for (int c = 0; c < chunks_a; ++c, ++ca, ra.next()) {
                     const int s = ra.pos;
-                    if (A_KMAJOR && F16) {
+                    if (A_KMAJOR && F16 && !a_img) {
                         // two boxes of 32 k x 128 rows, as they are in the caller's matrix; the transform warps make the
                         // slot's two FP16 images from them
                         if (ra.wrapped) ok = mbar_wait_bounded(&bars.raw_empty[s], ra.par ^ 1u, status);
@@ -232,7 +232,7 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
             if (!ok) {
                 // leaving early: boxes still in flight must have landed before this CTA's shared memory goes away
                 atomicOr(&bars.failed, 1u);
-                if (!USES_RAW)
+                if (!USES_RAW || a_img)
                     for (int c = max(0, ca - NR); c < ca; ++c) mbar_wait_bounded(&bars.full_a[c % NR], (unsigned)(c / NR) & 1u, status);
                 else
                     for (int c = max(0, ca - NRAW); c < ca; ++c) mbar_wait_bounded(&bars.raw_full[c % NRAW], (unsigned)(c / NRAW) & 1u, status);
@@ -497,10 +497,11 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const float4 m4 = mn_pre[s16 * 4 + j];
-                        const float p0 = __fadd_rn(__uint_as_float(r[4 * j]), __uint_as_float(q[4 * j]));
-                        const float p1 = __fadd_rn(__uint_as_float(r[4 * j + 1]), __uint_as_float(q[4 * j + 1]));
-                        const float p2 = __fadd_rn(__uint_as_float(r[4 * j + 2]), __uint_as_float(q[4 * j + 2]));
-                        const float p3 = __fadd_rn(__uint_as_float(r[4 * j + 3]), __uint_as_float(q[4 * j + 3]));
+                        float p0 = __fadd_rn(__uint_as_float(r[4 * j]), __uint_as_float(q[4 * j]));
+                        float p1 = __fadd_rn(__uint_as_float(r[4 * j + 1]), __uint_as_float(q[4 * j + 1]));
+                        float p2 = __fadd_rn(__uint_as_float(r[4 * j + 2]), __uint_as_float(q[4 * j + 2]));
+                        float p3 = __fadd_rn(__uint_as_float(r[4 * j + 3]), __uint_as_float(q[4 * j + 3]));
+                        if (F16) { p0 = __fmul_rn(p0, inv16); p1 = __fmul_rn(p1, inv16); p2 = __fmul_rn(p2, inv16); p3 = __fmul_rn(p3, inv16); }
                         const float4 o = make_float4(__fsub_rn(m4.x, p0), __fsub_rn(m4.y, p1), __fsub_rn(m4.z, p2), __fsub_rn(m4.w, p3));
                         any |= fabsf(o.x) > 1.1920928955078125e-07f || fabsf(o.y) > 1.1920928955078125e-07f ||
                                fabsf(o.z) > 1.1920928955078125e-07f || fabsf(o.w) > 1.1920928955078125e-07f;
@@ -521,7 +522,10 @@ __global__ void __launch_bounds__(NTH, 1) gemm_tc_tma_kernel(const __grid_consta
                 tmem_ld16(taddr, r);
                 if (!one_acc) tmem_ld16(taddr + acc_cols, q);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (F16) {                                           // hi * hi + (cross terms) / 2^11, and the operands' scales taken out
+                if (F16 && one_acc) {                                // one accumulator (low halves without their factor): the scales taken out
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__fmul_rn(__uint_as_float(r[j]), inv16));
+                } else if (F16) {                                    // hi * hi + (cross terms) / 2^11, and the operands' scales taken out
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         r[j] = __float_as_uint(__fmul_rn(__fmaf_rn(__uint_as_float(q[j]), 1.0f / kSplit16LoScale, __uint_as_float(r[j])), inv16));
@@ -648,16 +652,17 @@ cudaError_t gemm_tc_tma_launch(const GemmArgs &g, bool a_kmajor, unsigned *statu
     // innermost dimension first: K (then M) for an A contiguous along K, M (then K) otherwise
     const bool a_img = a_kmajor && g.a_image != nullptr;         // the map then covers the hi and lo matrices, one above the other
     const cuuint64_t dims[2] = {(cuuint64_t)(a_kmajor ? g.K : g.M), (cuuint64_t)(a_img ? 2 * g.a_image_rows : (a_kmajor ? g.M : g.K))};
-    const cuuint64_t strides[1] = {(cuuint64_t)(a_img ? g.K : g.lda) * sizeof(float)};
-    const cuuint32_t box[2] = {32, (cuuint32_t)(a_kmajor ? TM : KS)};
+    const bool img16 = a_img && g.f16;                           // ... of FP16 values: 64 k per 128-byte row of a box
+    const cuuint64_t strides[1] = {img16 ? (cuuint64_t)g.K * 2 : (cuuint64_t)(a_img ? g.K : g.lda) * sizeof(float)};
+    const cuuint32_t box[2] = {img16 ? 64u : 32u, (cuuint32_t)(a_kmajor ? TM : KS)};
     const cuuint32_t estr[2] = {1, 1};
     static const int l2 = [] { const char *e = std::getenv("BSQ_TMA_L2"); return e ? atoi(e) : 128; }();
-    if (encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, a_img ? g.a_image : const_cast<float *>(g.A), dims, strides, box, estr,
+    if (encode_tiled()(&map, img16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, a_img ? g.a_image : const_cast<float *>(g.A), dims, strides, box, estr,
                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                        l2 == 256 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : (l2 == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_128B),
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
-    const size_t smem = tma_smem_bytes(g.n_tile, (a_kmajor && !g.f16) ? 0 : g.raw_stages, g.a_stages, g.b_stages, g.f16);
+    const size_t smem = tma_smem_bytes(g.n_tile, ((a_kmajor && !g.f16) || a_img) ? 0 : g.raw_stages, g.a_stages, g.b_stages, g.f16);
     dim3 grid((g.M + TM - 1) / TM, (g.N + g.n_tile - 1) / g.n_tile, g.splits);
     if (g.persistent) {
         const int tiles = (int)(grid.x * grid.y);
