@@ -49,8 +49,8 @@ WORKLOAD = ("configs[4]: 32 independent 4096x14336 FP32 matrices, outlier_topk=0
             "U/V NF4, S FP32, error_correction_topk=0.01, compress+decompress, matrix i on rank i % N")
 # kernels this library launches per matrix in this configuration, counted from an ncu launch list of
 # `python bench.py --single C5A` (all launches of the run, minus the decompress calls', divided by the compress calls)
-LAUNCHES_PER_COMPRESS = 57
-LAUNCHES_PER_DECOMPRESS = 7
+LAUNCHES_PER_COMPRESS = 59
+LAUNCHES_PER_DECOMPRESS = 9
 
 
 def workloads():
