@@ -51,6 +51,9 @@ WORKLOAD = ("configs[4]: 32 independent 4096x14336 FP32 matrices, outlier_topk=0
 # `python bench.py --single C5A` (all launches of the run, minus the decompress calls', divided by the compress calls)
 LAUNCHES_PER_COMPRESS = 59
 LAUNCHES_PER_DECOMPRESS = 9
+# DRAM bytes of one 4096x14336x256 product launch of gemm_tc_tma_kernel (ncu, read + write): 239.8-242.7 MB for W X (matrix
+# read along M), 250.0-251.9 MB for W^T X (read along K); the matrix itself is 234.9 MB, so it is read once.
+PRODUCT_DRAM_BYTES_PER_LAUNCH = 245.7e6
 
 
 def workloads():
@@ -873,7 +876,9 @@ def main():
             "gpu_launches": (LAUNCHES_PER_COMPRESS + LAUNCHES_PER_DECOMPRESS) * n_layers * passes * nsteps,
             "roofline": {"bound": "tensor", "kernel": "gemm_tc_tma_kernel<*,256> (TMA-fed tcgen05, operands split into two %s halves: three MMAs per "
                                                        "product, 4096x14336 matrix times a 256-column panel)" % ("FP16" if split16 else "TF32"),
-                         "achieved": ach, "peak": peak3, "unit": "TFLOP/s", "frac": (ach / peak3) if ach else None, "traffic": None,
+                         "achieved": ach, "peak": peak3, "unit": "TFLOP/s", "frac": (ach / peak3) if ach else None, "traffic": PRODUCT_DRAM_BYTES_PER_LAUNCH,
+                         "traffic_unit": "bytes per launch: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel on this "
+                                         "matrix (FP16 halves), mean of the six products of a call; the matrix alone is 234.9 MB",
                          "peak_kind": ("FP16 dense matmul measured in this run (%.0f TFLOP/s) / 3; TF32 dense measured %.0f (achieved / (TF32 / 3) = %.2f); BF16 %s %.0f"
                                        % (fp16, tf32, (ach / (tf32 / 3.0)) if ach else 0.0, peak_kind, bf16_peak)) if split16 else
                                       "TF32 dense matmul measured in this run (%.0f TFLOP/s) / 3; BF16 %s %.0f" % (tf32, peak_kind, bf16_peak),
